@@ -45,7 +45,18 @@ def resolve(names) -> Architecture:
 
 
 def _load_builtin() -> None:
-    from ..models import lfm2  # noqa: F401  (registers itself on import)
+    from ..models import beledra, lfm2  # noqa: F401  (they register themselves on import)
+
+
+def architecture_names(raw: dict, cfg: dict | None = None):
+    """The names a config.json offers: ``architectures`` (a list, on either level) or ``architecture``
+    (one name)."""
+    cfg = raw if cfg is None else cfg
+    names = raw.get("architectures") or cfg.get("architectures")
+    if not names:
+        one = raw.get("architecture") or cfg.get("architecture")
+        names = [one] if isinstance(one, str) else None
+    return names
 
 
 def read_config_json(path) -> tuple[Architecture, Any, dict]:
@@ -58,7 +69,7 @@ def read_config_json(path) -> tuple[Architecture, Any, dict]:
         raise ConfigError(f"{file} does not exist")
     raw = json.loads(file.read_text())
     cfg = dict(raw.get("text_config", raw))
-    names = raw.get("architectures") or cfg.get("architectures")
+    names = architecture_names(raw, cfg)
     if not names:
         raise ConfigError(f"{file} names no architectures")
     arch = resolve(names)

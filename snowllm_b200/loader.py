@@ -28,9 +28,9 @@ def build_model(path_or_config, dtype="bfloat16") -> Model:
     """An unbound model (parts built, no weights) from a folder, a config.json or a raw dict."""
     dtype = parse_dtype(dtype)
     if isinstance(path_or_config, dict):
-        from .config.registry import resolve
+        from .config.registry import architecture_names, resolve
         raw = dict(path_or_config.get("text_config", path_or_config))
-        arch = resolve(path_or_config.get("architectures") or raw.get("architectures"))
+        arch = resolve(architecture_names(path_or_config, raw))
         raw["architectures"] = [arch.name]
         config = arch.read_config(raw)
     else:

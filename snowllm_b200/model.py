@@ -27,9 +27,12 @@ class Model:
         self.blocks = []
         for layer in spec.layers:
             block_cls = lookup("block", layer.block)
-            self.blocks.append(block_cls(_make("mixer", layer.mixer, dtype), _make("ffn", layer.ffn, dtype),
+            if (layer.ffn is None) != (layer.ffn_norm is None):
+                raise ConfigError("a layer has a feed-forward and its norm, or neither")
+            self.blocks.append(block_cls(_make("mixer", layer.mixer, dtype),
+                                         _make("ffn", layer.ffn, dtype) if layer.ffn is not None else None,
                                          _make("norm", layer.mixer_norm, dtype),
-                                         _make("norm", layer.ffn_norm, dtype)))
+                                         _make("norm", layer.ffn_norm, dtype) if layer.ffn_norm is not None else None))
         self.final_norm = _make("norm", spec.final_norm, dtype)
         self.head = _make("head", spec.head, dtype)
         self.run = list(spec.run)

@@ -80,6 +80,20 @@ _SIGNATURES = {
         "snk_norm_route_sort": [P, P, P, I, P, I, F, P, P, P, I, P, I, P, P, P, P, P, P, I, I, I, I, F, I, P, P],
         "snk_moe_combine": [P, P, P, P, I, I, I, P],
     },
+    "sublayer": {
+        "snk_norm_add": [P, P, P, I, P, I, I, F, I, P],
+        "snk_cast_rows": [P, P, LL, I, P],
+        "snk_gated_act": [P, P, I, I, I, I, I, P],
+        "snk_head_norm_gate": [P, I, I, F, P, I, P, I, LL, P, I, I, I, F, F, I, P],
+    },
+    "attention_split": {
+        "snk_split_prepare": [P, LL, I, I, I, P, P, I, I, F, P, I, F, P, P, P, I, I, P, P, P, I, I, I, I, I, I, I, I, P],
+        "snk_split_attention_tile_rows": [I, I],
+        "snk_split_attention": [P, P, P, P, I, I, P, P, P, I, I, P, I, I, I, I, I, I, I, F, P, I, I, P],
+    },
+    "mlstm": {
+        "snk_mlstm": [P, LL, I, I, I, I, I, P, P, I, F, P, P, P, P, P, P, P, I, I, I, I, P],
+    },
     "sampling": {
         "snk_argmax": [P, P, I, I, P],
         "snk_apply_penalties": [P, P, P, P, P, P, P, I, I, P],
@@ -1026,4 +1040,223 @@ def sample(logits, temperature, top_k, top_p, uniform, out=None):
     _chk(out, "sample output", torch.int32, (B,))
     check(fn("snk_sample")(_ptr(logits), _ptr(temperature), _ptr(top_k), _ptr(top_p), _ptr(uniform),
                            _ptr(out), B, V, _stream()), "sample", work=lambda: (_nbytes(logits), 0))
+    return out
+
+
+# --- layers with norms on the sublayers' outputs; gated heads ---------------------------
+
+ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2}
+
+
+def norm_add(residual, y, gamma, eps, dtype, x_out=None, want_x=True):
+    """``residual += y / sqrt(mean(y^2) + eps) * gamma`` over rows of float ``y``; returns the new
+    residual in the compute dtype (what the next sublayer reads), or None with ``want_x`` off."""
+    M, H = residual.shape
+    _chk(residual, "residual", torch.float32)
+    _chk(y, "sublayer output", torch.float32, (M, H))
+    g32 = _small(gamma, "norm weight", dtype)
+    _chk(gamma, "norm weight", shape=(H,))
+    if want_x and x_out is None:
+        x_out = torch.empty(M, H, dtype=dtype, device=residual.device)
+    if x_out is not None:
+        _chk(x_out, "norm_add output", dtype, (M, H))
+    check(fn("snk_norm_add")(_ptr(residual), _ptr(y), _ptr(gamma), g32, _ptr(x_out), M, H, float(eps),
+                             code_of(dtype), _stream()), "norm_add",
+          work=lambda: (3 * M * H * 4 + _nbytes(x_out, gamma), 0))
+    return x_out
+
+
+def cast_rows(x, dtype, out=None):
+    """Float ``x`` in the compute dtype."""
+    _chk(x, "cast input", torch.float32)
+    if out is None:
+        out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    _chk(out, "cast output", dtype, x.shape)
+    check(fn("snk_cast_rows")(_ptr(x), _ptr(out), x.numel(), code_of(dtype), _stream()), "cast_rows",
+          work=lambda: (_nbytes(x, out), 0))
+    return out
+
+
+def gated_act(gate_up, activation: str, interleaved: bool = False, out=None):
+    """[M, 2I] -> [M, I]: act(gate) * up with ``activation`` one of silu, relu, gelu_tanh.  Columns are
+    (gate | up), or with ``interleaved`` blocks of 8 gate columns followed by the 8 up columns."""
+    M, two_i = gate_up.shape
+    _chk(gate_up, "gated activation input", (torch.float32, torch.bfloat16))
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"activation {activation!r} (known: {', '.join(ACTIVATIONS)})")
+    if two_i % 2:
+        raise KernelError("gated activation input needs an even width")
+    inter = two_i // 2
+    if out is None:
+        out = torch.empty(M, inter, dtype=gate_up.dtype, device=gate_up.device)
+    _chk(out, "gated activation output", gate_up.dtype, (M, inter))
+    check(fn("snk_gated_act")(_ptr(gate_up), _ptr(out), M, inter, int(interleaved), ACTIVATIONS[activation],
+                              code_of(gate_up.dtype), _stream()), "gated_act",
+          work=lambda: (_nbytes(gate_up, out), 0))
+    return out
+
+
+def head_norm_gate(a, heads, dv, eps, dtype, *, second=0, lam=0.0, weight=None, gate=None, gate_col=0,
+                   mult=1.0, out=None):
+    """Per (row, head): o = a[..., :dv] - lam * a[..., second:second + dv] (the second term only with
+    ``second``), o / sqrt(mean(o^2) + eps) * mult, times ``weight`` [heads*dv] and times
+    sigmoid(gate[:, gate_col + head*dv + c]) where given.  ``a``: float [M, heads, width]; ``gate``: a
+    2-D float or compute-dtype tensor whose columns from ``gate_col`` on hold the gate's pre-activation."""
+    _chk(a, "head values", torch.float32)
+    M = a.shape[0]
+    stride = a.numel() // max(M * heads, 1)
+    if a.numel() != M * heads * stride or stride < dv + second:
+        raise KernelError(f"head values of shape {tuple(a.shape)} do not hold {heads} heads of {dv}")
+    w32 = 0
+    if weight is not None:
+        w32 = _small(weight, "head norm weight", dtype)
+        _chk(weight, "head norm weight", shape=(heads * dv,))
+    g_ptr, g32, g_ld = c_void_p(0), 0, 0
+    if gate is not None:
+        _chk(gate, "gate", (torch.float32, dtype))
+        if gate.dim() != 2 or gate.shape[0] != M or gate.shape[1] < gate_col + heads * dv:
+            raise KernelError(f"gate of shape {tuple(gate.shape)} has no {heads * dv} columns from {gate_col} on")
+        g32, g_ld = int(gate.dtype == torch.float32), gate.shape[1]
+        g_ptr = c_void_p(gate.data_ptr() + gate_col * gate.element_size())
+    if out is None:
+        out = torch.empty(M, heads * dv, dtype=dtype, device=a.device)
+    _chk(out, "gated heads", dtype, (M, heads * dv))
+    check(fn("snk_head_norm_gate")(_ptr(a), stride, int(second), float(lam), _ptr(weight), w32, g_ptr, g32, g_ld,
+                                   _ptr(out), M, heads, dv, float(eps), float(mult), code_of(dtype), _stream()),
+          "head_norm_gate", work=lambda: (_nbytes(a, out) + M * heads * dv * (gate.element_size() if gate is not None else 0), 0))
+    return out
+
+
+# --- attention over split pools ---------------------------------------------------------------
+
+def split_prepare(proj, q_off, k_off, v_off, q_gamma, k_gamma, eps, inv_freq, rot_dim, rot_mult, positions,
+                  row_seg, block_table, page_size, kpool, vpool, nq, nkv, maps, dk, dv, write_kv=True):
+    """Rows of a fused projection ``proj`` [M, width] (q at column ``q_off`` as [nq, dk], k at ``k_off`` as
+    [nkv*maps, dk], v at ``v_off`` as [nkv, dv]): per-head RMS norm of q and k (if weights are given),
+    rotation of the first ``rot_dim`` elements of each head by angle position * inv_freq with cos and sin
+    times ``rot_mult`` (if ``inv_freq``), k and v written to their pools
+    ([pages, nkv, page_size, maps*dk] and [pages, nkv, page_size, dv]); returns q [M, nq, dk]."""
+    M, width = proj.shape
+    dtype = proj.dtype
+    _chk(proj, "projection", (torch.float32, torch.bfloat16))
+    need = max(q_off + nq * dk, (k_off + nkv * maps * dk) if write_kv else 0, (v_off + nkv * dv) if write_kv else 0)
+    if width < need:
+        raise KernelError(f"projection of width {width} holds no {need} columns")
+    has_norm = q_gamma is not None
+    g32 = 0
+    if has_norm:
+        g32 = _small(q_gamma, "q norm weight", dtype)
+        if _small(k_gamma, "k norm weight", dtype) != g32:
+            raise KernelError("q and k norm weights must share a dtype")
+        _chk(q_gamma, "q norm weight", shape=(dk,))
+        _chk(k_gamma, "k norm weight", shape=(dk,))
+    rot = int(rot_dim) if inv_freq is not None else 0
+    if inv_freq is not None:
+        _chk(inv_freq, "inv_freq", torch.float32, (rot // 2,))
+    _chk(positions, "positions", torch.int32, (M,))
+    _chk(row_seg, "row_seg", torch.int32, (M,))
+    _chk(block_table, "block table", torch.int32)
+    if write_kv:
+        _chk(kpool, "key pool", dtype)
+        _chk(vpool, "value pool", dtype)
+        if tuple(kpool.shape[1:]) != (nkv, page_size, maps * dk) or tuple(vpool.shape[1:]) != (nkv, page_size, dv):
+            raise KernelError(f"pools of shapes {tuple(kpool.shape)} and {tuple(vpool.shape)}, want [pages, {nkv}, "
+                              f"{page_size}, {maps * dk}] and [pages, {nkv}, {page_size}, {dv}]")
+    q_out = torch.empty(M, nq, dk, dtype=dtype, device=proj.device)
+    check(fn("snk_split_prepare")(
+        _ptr(proj), width, q_off, k_off, v_off, _ptr(q_gamma), _ptr(k_gamma), g32, int(has_norm), float(eps),
+        _ptr(inv_freq), rot, float(rot_mult), _ptr(positions), _ptr(row_seg), _ptr(block_table),
+        block_table.shape[1], page_size, _ptr(kpool), _ptr(vpool), _ptr(q_out), M, nq, nkv * maps, nkv, dk, dv,
+        int(write_kv), code_of(dtype), _stream()), "split_prepare",
+        work=lambda: (2 * M * need * proj.element_size(), 0))
+    return q_out
+
+
+def split_attention_tile_rows(heads_per_kv: int, decode_only: bool) -> int:
+    """Rows of one request that a block of ``split_attention`` serves (0: too many heads per kv head)."""
+    return int(fn("snk_split_attention_tile_rows")(int(heads_per_kv), int(decode_only)))
+
+
+def split_attention(q, kpool, vpool, block_table, page_size, positions, row_seg, scale, *, maps=1, window=None,
+                    bias=None, tiles=None, tile_rows=1, out_dtype=None, out=None):
+    """Causal attention of q [M, nq, dk] (nq = heads * maps) over keys [pages, nkv, page_size, maps*dk] and
+    values [pages, nkv, page_size, dv]; query head (h, map) reads the key at offset map*dk of its kv head.
+    ``window``: the last ``window`` keys only.  ``bias`` float [nq, L]: added to the scaled score by
+    distance min(i - j, L - 1).  ``tiles`` int32 [n, 2] = (first row, rows <= tile_rows) of consecutive
+    rows of one request, covering the step; None: every row alone.  Scores, weights and sums are float;
+    returns [M, nq, dv] in ``out_dtype`` (float32 or the compute dtype)."""
+    M, nq, dk = q.shape
+    dtype = q.dtype
+    _chk(q, "q", (torch.float32, torch.bfloat16))
+    _chk(kpool, "key pool", dtype)
+    _chk(vpool, "value pool", dtype)
+    nkv, dv = vpool.shape[1], vpool.shape[3]
+    if kpool.dim() != 4 or tuple(kpool.shape[1:]) != (nkv, page_size, maps * dk) or vpool.shape[2] != page_size:
+        raise KernelError(f"key pool {tuple(kpool.shape)} and value pool {tuple(vpool.shape)} do not fit "
+                          f"{nkv} kv heads, pages of {page_size} and {maps} maps of {dk}")
+    _chk(positions, "positions", torch.int32, (M,))
+    _chk(row_seg, "row_seg", torch.int32, (M,))
+    _chk(block_table, "block table", torch.int32)
+    if bias is not None:
+        _chk(bias, "distance bias", torch.float32)
+        if bias.dim() != 2 or bias.shape[0] != nq:
+            raise KernelError(f"distance bias of shape {tuple(bias.shape)}, want [{nq}, distances]")
+    n_tiles = M
+    if tiles is not None:
+        _chk(tiles, "attention tiles", torch.int32)
+        if tiles.dim() != 2 or tiles.shape[1] != 2:
+            raise KernelError("attention tiles must be [n, 2]")
+        n_tiles = tiles.shape[0]
+    out_dtype = out_dtype or dtype
+    if out_dtype not in (dtype, torch.float32):
+        raise KernelError("attention output is the compute dtype or float32")
+    if out is None:
+        out = torch.empty(M, nq, dv, dtype=out_dtype, device=q.device)
+    _chk(out, "attention output", out_dtype, (M, nq, dv))
+
+    def work():
+        pos = positions.cpu().long()
+        keys = (pos + 1).clamp(max=int(window)) if window else pos + 1
+        total = int(keys.sum())
+        return (-(-total // max(tile_rows, 1)) * nkv * (maps * dk + dv) * kpool.element_size() + _nbytes(q, out),
+                2 * nq * (dk + dv) * total)
+    check(fn("snk_split_attention")(
+        _ptr(q), _ptr(kpool), _ptr(vpool), _ptr(block_table), block_table.shape[1], page_size, _ptr(positions),
+        _ptr(row_seg), _ptr(tiles), n_tiles, int(tile_rows), _ptr(out), int(out_dtype == torch.float32 and dtype != torch.float32),
+        nq, nkv, int(maps), dk, dv, int(window or 0), float(scale), _ptr(bias),
+        bias.shape[1] if bias is not None else 0, code_of(dtype), _stream()), "split_attention", work=work)
+    return out
+
+
+# --- matrix memory --------------------------------------------------------------------------------
+
+def mlstm(proj, q_off, k_off, v_off, i_off, f_off, bias_i, bias_f, cap, cu_seqlens, seg_start, seg_slot,
+          state_s, state_n, state_m, heads, dk, dv, out=None):
+    """The mLSTM recurrence over the segments of a flat batch.  ``proj``: float [M, width] with q, k
+    ([heads, dk]), v ([heads, dv]) and the input and forget gates' pre-activations ([heads] each) at the
+    given columns.  The states (float; [slots, heads, dk, dv], [slots, heads, dk], [slots, heads]) are read
+    unless a segment starts at 0, and brought up to date.  Returns the raw head outputs, float [M, heads*dv]."""
+    M, width = proj.shape
+    _chk(proj, "mlstm projection", torch.float32)
+    B = seg_start.numel()
+    _chk(cu_seqlens, "cu_seqlens", torch.int32, (B + 1,))
+    _chk(seg_start, "seg_start", torch.int32, (B,))
+    _chk(seg_slot, "seg_slot", torch.int32, (B,))
+    slots = state_s.shape[0]
+    _chk(state_s, "mlstm matrix state", torch.float32, (slots, heads, dk, dv))
+    _chk(state_n, "mlstm vector state", torch.float32, (slots, heads, dk))
+    _chk(state_m, "mlstm maximum state", torch.float32, (slots, heads))
+    if width < max(q_off + heads * dk, k_off + heads * dk, v_off + heads * dv, i_off + heads, f_off + heads):
+        raise KernelError(f"mlstm projection of width {width} is too narrow")
+    b32 = _small(bias_i, "input gate bias", torch.float32)
+    if _small(bias_f, "forget gate bias", torch.float32) != b32:
+        raise KernelError("gate biases must share a dtype")
+    if out is None:
+        out = torch.empty(M, heads * dv, dtype=torch.float32, device=proj.device)
+    _chk(out, "mlstm output", torch.float32, (M, heads * dv))
+    check(fn("snk_mlstm")(_ptr(proj), width, q_off, k_off, v_off, i_off, f_off, _ptr(bias_i), _ptr(bias_f), b32,
+                          float(cap), _ptr(cu_seqlens), _ptr(seg_start), _ptr(seg_slot), _ptr(state_s),
+                          _ptr(state_n), _ptr(state_m), _ptr(out), B, heads, dk, dv, _stream()), "mlstm",
+          work=lambda: (M * (2 * heads * dk + 2 * heads * dv) * 4 + 2 * B * heads * dk * dv * 4,
+                        4 * M * heads * dk * dv))
     return out

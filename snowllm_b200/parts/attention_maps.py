@@ -1,0 +1,257 @@
+"""Windowed grouped-query attention mixers whose keys and values have widths of their own
+(csrc/attention_split.cu): keys of ``head_dim``, values of ``v_head_dim``, kept in two pools.
+
+Two kinds are built on one class:
+
+* ``bias_attention``: one softmax map per head; a learned bias is added to the scaled score, chosen by
+  head and by a bucket of the distance i - j (``DistanceBuckets``).  No rotation.
+* ``diff_attention``: two softmax maps per head over the same values (q and k hold the maps' halves side
+  by side, head by head); the second map's output is taken off the first with one weight per layer,
+  lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + offset; each head of the difference is divided by its root
+  mean square and scaled by (1 - offset); the heads are gated by sigmoid(W_g x) before the output
+  product.  Rotary positions (plain or stretched) on the first ``rot_dim`` elements of every map.
+
+Both: per-head RMS norm of q and k with one weight of ``head_dim`` shared by all heads (and maps), before
+the rotation; ``window`` keeps the last ``window`` keys.  Scores, softmax weights and the per-head
+statistics are float whatever the compute dtype.  A layer that reads another layer's cache
+(``reads_cache``) has no key and value tensors at all: it projects q (and the gate) alone and attends
+over the keys as the owner wrote them.  ``cache_window`` is how many positions the owner of the cache
+keeps: its own window or the widest window among its readers."""
+from __future__ import annotations
+
+import math
+
+import numpy as np
+import torch
+
+from ..errors import ConfigError, KernelError
+from ..ops import kernels, linear
+from .base import Part
+from .registry import lookup, register_mixer
+from .spec import INIT_ONES, KEEP_F32, KEEP_SMALL, PagedKVSpec, TensorSpec
+
+
+class DistanceBuckets:
+    """Which row of a bias table a key ``n`` positions back reads: one row per distance below rows/2, then
+    logarithmic steps that reach the last row at distance ``far``:
+    bucket(n) = n for n < rows/2, else min(rows - 1, rows/2 + floor(ln(n / (rows/2)) / ln(far / (rows/2))
+    * (rows - rows/2))).  From some distance on the bucket is the last row."""
+
+    def __init__(self, rows: int, far: float):
+        if rows < 2 or far <= rows // 2:
+            raise ConfigError(f"a distance bias of {rows} rows reaching to {far}: want rows >= 2 and far > rows/2")
+        self.rows, self.far = int(rows), float(far)
+
+    def bucket(self, n: int) -> int:
+        half = self.rows // 2
+        if n < half:
+            return n
+        # the logarithms in double precision; an exact step (n/half a whole power of the ratio) must not
+        # fall below its bucket by a rounding error
+        step = math.log(n / half) / math.log(self.far / half) * (self.rows - half)
+        return min(self.rows - 1, half + int(math.floor(step + 1e-9)))
+
+    def saturation(self) -> int:
+        """The first distance whose bucket is the last row (every longer distance reads it too)."""
+        n = self.rows // 2
+        while self.bucket(n) < self.rows - 1:
+            n += 1
+        return n
+
+    def table(self, length: int) -> list:
+        return [self.bucket(n) for n in range(length)]
+
+
+def pad_rows(w: torch.Tensor, multiple: int) -> torch.Tensor:
+    extra = -w.shape[0] % multiple
+    if not extra:
+        return w.contiguous()
+    return torch.cat((w, w.new_zeros(extra, w.shape[1])), 0).contiguous()
+
+
+def attention_tiles(ctx, tile_rows: int):
+    """The step's rows cut into runs of up to ``tile_rows`` consecutive rows of one request: int32 [n, 2] =
+    (first row, rows) on the device, uploaded once per step; None when every row stands alone (decode
+    steps: a captured step then holds nothing that changes)."""
+    if tile_rows <= 1 or max(ctx.host_seg_len) <= 1:
+        return None
+    key = ("attention_maps_tiles", tile_rows)
+    if key not in ctx.memo:
+        tiles, first = [], 0
+        for n in ctx.host_seg_len:
+            for r in range(0, n, tile_rows):
+                tiles.append((first + r, min(tile_rows, n - r)))
+            first += n
+        host = torch.tensor(tiles, dtype=torch.int32).pin_memory()
+        ctx.memo[key] = host.to(ctx.device, non_blocking=True)
+    return ctx.memo[key]
+
+
+class MapsAttention(Part):
+    libraries = ("gemm", "gemm_skinny", "gemm_tc", "gemm_tc2", "attention_split", "sublayer")
+    maps = 1
+
+    def __init__(self, dtype, names, *, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 v_head_dim: int, scale: float, qk_norm_eps: float | None, window: int | None = None,
+                 cache_window: int | None = None, position: dict | None = None, reads_cache: bool = False):
+        super().__init__(dtype, names)
+        if num_heads % num_kv_heads:
+            raise ConfigError(f"num_heads={num_heads} is no multiple of num_kv_heads={num_kv_heads}")
+        if (num_heads // num_kv_heads) * self.maps > 32:
+            raise ConfigError(f"{num_heads // num_kv_heads} query heads per kv head with {self.maps} maps: "
+                              f"the attention kernel serves up to 32 per kv head")
+        if v_head_dim > 256:
+            raise ConfigError(f"v_head_dim={v_head_dim}: the attention kernel takes up to 256")
+        self.hidden_size, self.num_heads, self.num_kv_heads = hidden_size, num_heads, num_kv_heads
+        self.head_dim, self.v_head_dim, self.scale = head_dim, v_head_dim, float(scale)
+        self.qk_norm_eps, self.window, self.reads_cache = qk_norm_eps, window, reads_cache
+        self.cache_window = cache_window if cache_window is not None or window is None else window
+        if window is None and cache_window is not None:
+            raise ConfigError("a layer that sees every key cannot live on a cache that keeps a window")
+        if window is not None and self.cache_window is not None and self.cache_window < window:
+            raise ConfigError(f"cache_window={cache_window} is shorter than the layer's window {window}")
+        pos = dict(position or {"kind": "none"})
+        self.position = lookup("position", pos.pop("kind"))(**pos)
+        self.w_in = self.wo = self.q_norm = self.k_norm = None
+        self.bias = None
+
+    # -- sizes of the fused projection ----------------------------------------------------------
+    @property
+    def nq(self) -> int:
+        return self.num_heads * self.maps
+
+    def _columns(self):
+        """(q, k, v, gate) column offsets of the fused projection, and its width."""
+        q = 0
+        k = q + self.nq * self.head_dim
+        v = k + (0 if self.reads_cache else self.num_kv_heads * self.maps * self.head_dim)
+        g = v + (0 if self.reads_cache else self.num_kv_heads * self.v_head_dim)
+        return q, k, v, g, g + self._gate_width()
+
+    def _gate_width(self) -> int:
+        return 0
+
+    def cache_spec(self):
+        return PagedKVSpec(self.num_kv_heads, self.maps * self.head_dim, self.cache_window, self.v_head_dim,
+                           separate=True)
+
+    def declare(self, has):
+        H, dk, dv, n = self.hidden_size, self.head_dim, self.v_head_dim, self.names
+        specs = [TensorSpec("q_proj", n["q_proj"], (self.nq * dk, H))]
+        if not self.reads_cache:
+            specs += [TensorSpec("k_proj", n["k_proj"], (self.num_kv_heads * self.maps * dk, H)),
+                      TensorSpec("v_proj", n["v_proj"], (self.num_kv_heads * dv, H))]
+        specs.append(TensorSpec("out_proj", n["out_proj"], (H, self.num_heads * dv)))
+        if self.qk_norm_eps is not None:
+            specs.append(TensorSpec("q_norm", n["q_norm"], (dk,), INIT_ONES, KEEP_SMALL))
+            if not self.reads_cache:
+                specs.append(TensorSpec("k_norm", n["k_norm"], (dk,), INIT_ONES, KEEP_SMALL))
+        return specs
+
+    def _projection_rows(self, tensors) -> list:
+        rows = [tensors["q_proj"]]
+        if not self.reads_cache:
+            rows += [tensors["k_proj"], tensors["v_proj"]]
+        return rows
+
+    def bind(self, tensors):
+        self.w_in = pad_rows(torch.cat(self._projection_rows(tensors), 0), 16)
+        self.wo = tensors["out_proj"]
+        self.q_norm = tensors.get("q_norm")
+        self.k_norm = tensors.get("k_norm", self.q_norm)      # a reader of another layer's cache normalises q alone
+
+    # -- the step -----------------------------------------------------------------------------
+    def _attend(self, ctx, x, cache, owns_cache, out_dtype):
+        if owns_cache == self.reads_cache:
+            raise KernelError("a layer without key and value tensors must read another layer's cache, "
+                              "and one with them must own its cache")
+        proj = linear(x, self.w_in)
+        q_off, k_off, v_off, _, _ = self._columns()
+        kpool, vpool = cache.pools
+        inv_freq, rot_dim = self.position.rotary(x.device)
+        q = kernels.split_prepare(proj, q_off, k_off, v_off, self.q_norm, self.k_norm, self.qk_norm_eps or 0.0,
+                                  inv_freq, rot_dim, getattr(self.position, "magnitude", 1.0), ctx.positions,
+                                  ctx.row_seg, cache.block_table, cache.page_size, kpool, vpool, self.nq,
+                                  self.num_kv_heads, self.maps, self.head_dim, self.v_head_dim,
+                                  write_kv=owns_cache)
+        ctx.tap("attention_q", q)
+        decode_only = max(ctx.host_seg_len) <= 1
+        tile_rows = kernels.split_attention_tile_rows(self.nq // self.num_kv_heads, decode_only)
+        out = kernels.split_attention(q, kpool, vpool, cache.block_table, cache.page_size, ctx.positions,
+                                      ctx.row_seg, self.scale, maps=self.maps, window=self.window, bias=self.bias,
+                                      tiles=attention_tiles(ctx, tile_rows), tile_rows=tile_rows,
+                                      out_dtype=out_dtype)
+        ctx.tap("attention_o", out)
+        return proj, out
+
+
+class BiasAttention(MapsAttention):
+    """One map per head and a learned bias per (distance bucket, head)."""
+
+    DEFAULT_ROWS = 32          # rows of a drawn table when the configuration names none
+
+    def __init__(self, dtype, names, *, bias_far: float, bias_rows: int | None = None, **kw):
+        super().__init__(dtype, names, **kw)
+        self.bias_rows, self.bias_far = bias_rows, float(bias_far)
+        self.buckets = None
+
+    def declare(self, has):
+        # the table's rows are the checkpoint's to say (its first dimension), unless the configuration does
+        rows = self.bias_rows if self.bias_rows is not None else -1
+        return super().declare(has) + [TensorSpec("rel", self.names["rel"], (rows, self.num_heads), keep=KEEP_F32,
+                                                  free_default=self.DEFAULT_ROWS)]
+
+    def bind(self, tensors):
+        super().bind(tensors)
+        self.buckets = DistanceBuckets(tensors["rel"].shape[0], self.bias_far)
+        # the bias by distance: [heads, L] with L the window, or where the buckets reach their last row
+        length = self.buckets.saturation() + 1
+        if self.window is not None:
+            length = min(length, self.window)
+        rel = tensors["rel"].float()
+        index = torch.as_tensor(np.asarray(self.buckets.table(length), dtype=np.int64), device=rel.device)
+        self.bias = rel[index].t().contiguous()
+
+    def forward(self, ctx, x, cache, owns_cache=True):
+        _, out = self._attend(ctx, x, cache, owns_cache, self.dtype)
+        return linear(out.view(ctx.M, -1), self.wo, out_dtype=torch.float32)
+
+
+class DiffAttention(MapsAttention):
+    """Two maps per head; the second is taken off the first; normalised, gated heads."""
+    maps = 2
+
+    def __init__(self, dtype, names, *, offset: float, head_norm_eps: float, **kw):
+        super().__init__(dtype, names, **kw)
+        self.offset, self.head_norm_eps = float(offset), float(head_norm_eps)
+        self.lam = None
+
+    def _gate_width(self) -> int:
+        return self.num_heads * self.v_head_dim
+
+    def declare(self, has):
+        n, dk = self.names, self.head_dim
+        return super().declare(has) + [
+            TensorSpec("gate_proj", n["gate_proj"], (self.num_heads * self.v_head_dim, self.hidden_size)),
+            *(TensorSpec(v, n[v], (dk,), keep=KEEP_F32) for v in ("lq1", "lk1", "lq2", "lk2"))]
+
+    def _projection_rows(self, tensors) -> list:
+        return super()._projection_rows(tensors) + [tensors["gate_proj"]]
+
+    def bind(self, tensors):
+        super().bind(tensors)
+        t = {k: tensors[k].float() for k in ("lq1", "lk1", "lq2", "lk2")}
+        self.lam = float(torch.exp((t["lq1"] * t["lk1"]).sum()) - torch.exp((t["lq2"] * t["lk2"]).sum())) + self.offset
+
+    def forward(self, ctx, x, cache, owns_cache=True):
+        proj, maps = self._attend(ctx, x, cache, owns_cache, torch.float32)     # [M, heads * 2, dv] float
+        dv = self.v_head_dim
+        gate_col = self._columns()[3]
+        heads = kernels.head_norm_gate(maps, self.num_heads, dv, self.head_norm_eps, self.dtype, second=dv,
+                                       lam=self.lam, gate=proj, gate_col=gate_col, mult=1.0 - self.offset)
+        ctx.tap("attention_heads", heads)
+        return linear(heads, self.wo, out_dtype=torch.float32)
+
+
+register_mixer("bias_attention", BiasAttention)
+register_mixer("diff_attention", DiffAttention)

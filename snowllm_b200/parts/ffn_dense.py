@@ -5,7 +5,8 @@ from __future__ import annotations
 
 import torch
 
-from ..ops import interleave_gate_up, linear, linear_swiglu
+from ..errors import ConfigError
+from ..ops import interleave_gate_up, kernels, linear, linear_swiglu
 from .base import Part
 from .registry import register_ffn
 from .spec import TensorSpec
@@ -37,4 +38,23 @@ class SwiGLU(Part):
         return linear(act, self.w2, out_dtype=torch.float32)
 
 
+class GatedFFN(SwiGLU):
+    """down(act(gate x) * up x) with ``activation`` one of silu, relu, gelu_tanh.  silu is the class
+    above (the products apply it at their store); the others run the fused gate|up product and then one
+    elementwise kernel."""
+
+    def __init__(self, dtype, names, *, hidden_size: int, intermediate_size: int, activation: str = "silu"):
+        super().__init__(dtype, names, hidden_size=hidden_size, intermediate_size=intermediate_size)
+        if activation not in kernels.ACTIVATIONS:
+            raise ConfigError(f"activation {activation!r} (known: {', '.join(kernels.ACTIVATIONS)})")
+        self.activation = activation
+
+    def forward(self, ctx, x):
+        if self.activation == "silu":
+            return super().forward(ctx, x)
+        act = kernels.gated_act(linear(x, self.w13), self.activation, self.interleaved)
+        return linear(act, self.w2, out_dtype=torch.float32)
+
+
 register_ffn("swiglu", SwiGLU)
+register_ffn("gated", GatedFFN)

@@ -29,5 +29,12 @@ class RMSNorm(Part):
         ``rows`` (int32 row numbers) only those rows come out and the residual stays untouched."""
         return kernels.add_rmsnorm(residual, delta, self.weight, self.eps, self.dtype, rows=rows)
 
+    def add_normed(self, ctx, residual, y):
+        """``residual += norm(y)`` for a sublayer's float output ``y`` (the norm on the output side);
+        returns the new residual in the compute dtype (the residual itself when that is float)."""
+        same = residual.dtype == self.dtype
+        x = kernels.norm_add(residual, y, self.weight, self.eps, self.dtype, want_x=not same)
+        return residual if same else x
+
 
 register_norm("rmsnorm", RMSNorm)

@@ -32,6 +32,8 @@ class TensorSpec:
     init: str = INIT_NORMAL
     keep: str = KEEP_COMPUTE
     file_shape: tuple[int, ...] | None = None   # shape as stored, when it differs (a view)
+    free_default: int | None = None             # a dimension given as -1 is the file's to choose; drawn
+                                                # weights take this size for it
 
     @property
     def stored_shape(self) -> tuple[int, ...]:
@@ -51,9 +53,9 @@ class LayerSpec:
     """One layer: how its parts are arranged (block) and which parts they are."""
     block: str                      # arrangement kind, e.g. "prenorm"
     mixer: PartSpec
-    ffn: PartSpec
+    ffn: PartSpec | None            # None (with ffn_norm None): a layer of the mixer's sublayer alone
     mixer_norm: PartSpec
-    ffn_norm: PartSpec
+    ffn_norm: PartSpec | None
 
 
 @dataclass(frozen=True)
@@ -90,16 +92,19 @@ class PagedKVSpec:
     Keys and values of one width lie in one tensor [pages, 2, kv heads, page_size, head_dim].  With
     ``v_head_dim`` of another width they are two tensors [pages, kv heads, page_size, width]; with
     ``v_head_dim`` 0 there is the key tensor alone (a latent row per position, a cache of keys only).
+    ``separate`` asks for the two tensors also where the widths happen to be equal (a kernel that reads
+    keys and values from pools of their own).
     ``cache_dtype`` None keeps the rows in the compute dtype; "float32" or "bfloat16" fixes it."""
     num_kv_heads: int
     head_dim: int
     window: int | None = None
     v_head_dim: int | None = None
     cache_dtype: str | None = None
+    separate: bool = False
 
     @property
     def fused(self) -> bool:
-        return self.v_head_dim is None or self.v_head_dim == self.head_dim
+        return not self.separate and (self.v_head_dim is None or self.v_head_dim == self.head_dim)
 
     def pool_shapes(self, num_pages: int, page_size: int) -> tuple:
         if self.fused:

@@ -26,6 +26,11 @@ def kept_dtype(spec: TensorSpec, stored: torch.dtype, compute: torch.dtype) -> t
     return compute
 
 
+def _shape_fits(shape, want) -> bool:
+    """Equal shapes; a wanted dimension of -1 takes any size."""
+    return len(shape) == len(want) and all(w == -1 or int(a) == int(w) for a, w in zip(shape, want))
+
+
 def check_against(declared: list[TensorSpec], names, meta) -> None:
     """Raise one WeightError that lists everything wrong, or return."""
     wanted = {s.name: s for s in declared}
@@ -37,7 +42,7 @@ def check_against(declared: list[TensorSpec], names, meta) -> None:
         if n not in have:
             continue
         dtype, shape = meta(n)
-        if tuple(shape) not in (tuple(s.stored_shape), tuple(s.shape)):
+        if not any(_shape_fits(shape, want) for want in (s.stored_shape, s.shape)):
             wrong.append(f"{n}: shape {tuple(shape)}, want {tuple(s.stored_shape)}")
         elif s.keep == KEEP_I32 and dtype in _FLOATS:
             wrong.append(f"{n}: dtype {dtype}, want an integer table")

@@ -27,7 +27,7 @@ def random_tensors(model, seed: int, dtype: torch.dtype = torch.bfloat16, std: f
     gen = torch.Generator(device=device).manual_seed(seed)
     out = {}
     for _, spec in model.declare(lambda name: False):
-        shape = spec.stored_shape
+        shape = tuple(spec.free_default if d == -1 else d for d in spec.stored_shape)
         if spec.keep == KEEP_I32:
             t = torch.zeros(shape, dtype=torch.int32, device=device)
         elif spec.init == INIT_ONES:
