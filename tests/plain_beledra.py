@@ -13,6 +13,16 @@ import math
 import torch
 
 
+# Where the 16-bit path stores a value (a sublayer's input, a projection's output, what enters the output
+# product), the rounding variant of this implementation rounds it to bfloat16 and goes on in ``dtype``: how
+# far that moves the logits is the measure of what rounding alone may cost.
+ROUND = {"on": False}
+
+
+def stored(x):
+    return x.to(torch.bfloat16).to(x.dtype) if ROUND["on"] else x
+
+
 def rms_normalise(x, eps):
     return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps)
 
@@ -29,7 +39,8 @@ ACTIVATIONS = {"relu": torch.relu, "gelu_tanh": gelu_tanh, "silu": torch.nn.func
 
 
 def gated_ff(h, gate, up, down, act="relu"):
-    return (ACTIVATIONS[act](h @ gate.T) * (h @ up.T)) @ down.T
+    h = stored(h)
+    return stored(ACTIVATIONS[act](stored(h @ gate.T)) * stored(h @ up.T)) @ down.T
 
 
 # --- distance bias --------------------------------------------------------------------------------
@@ -58,11 +69,12 @@ def biased_attention(h, t, p, m, eps):
     bucket and head.  ``t``: the layer's mixer tensors by short name; ``m``: the mixer's config."""
     T = h.shape[0]
     H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = (h @ t["q"].T).view(T, H, dk)
-    k = (h @ t["k"].T).view(T, G, dk)
-    v = (h @ t["v"].T).view(T, G, dv)
-    q = rms_norm(q, t["q.norm"], eps)
-    k = rms_norm(k, t["k.norm"], eps)
+    h = stored(h)
+    q = stored(h @ t["q"].T).view(T, H, dk)
+    k = stored(h @ t["k"].T).view(T, G, dk)
+    v = stored(h @ t["v"].T).view(T, G, dv)
+    q = stored(rms_norm(q, t["q.norm"], eps))
+    k = stored(rms_norm(k, t["k.norm"], eps))
     ok, d = window_mask(T, (m.get("mask") or {}).get("size"))
     rel = t["rel"]
     rows = rel.shape[0]
@@ -74,7 +86,7 @@ def biased_attention(h, t, p, m, eps):
         s = (q[:, head] @ k[:, g].T) * m["scale"] + rel[bucket, head]
         s = s.masked_fill(~ok, -math.inf)
         out[:, head] = torch.softmax(s, -1) @ v[:, g]
-    return out.reshape(T, H * dv) @ t["o"].T
+    return stored(out.reshape(T, H * dv)) @ t["o"].T
 
 
 # --- rotary positions with YaRN -------------------------------------------------------------------
@@ -115,9 +127,10 @@ def rotate(x, positions, rot):
 def differential_keys_values(h, t, m, eps, positions):
     T = h.shape[0]
     G, dk, dv = m["kv_heads"], m["dim"], m["vdim"]
-    k = (h @ t["k"].T).view(T, G * 2, dk)
-    k = rotate(rms_norm(k, t["k.norm"], eps), positions, m.get("rot"))
-    return k.view(T, G, 2, dk), (h @ t["v"].T).view(T, G, dv)
+    h = stored(h)
+    k = stored(h @ t["k"].T).view(T, G * 2, dk)
+    k = stored(rotate(rms_norm(k, t["k.norm"], eps), positions, m.get("rot")))
+    return k.view(T, G, 2, dk), stored(h @ t["v"].T).view(T, G, dv)
 
 
 def differential_attention(h, t, m, eps, kv):
@@ -126,8 +139,9 @@ def differential_attention(h, t, m, eps, kv):
     T = h.shape[0]
     H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
     positions = torch.arange(T)
-    q = (h @ t["q"].T).view(T, H * 2, dk)
-    q = rotate(rms_norm(q, t["q.norm"], eps), positions, m.get("rot")).view(T, H, 2, dk)
+    h = stored(h)
+    q = stored(h @ t["q"].T).view(T, H * 2, dk)
+    q = stored(rotate(rms_norm(q, t["q.norm"], eps), positions, m.get("rot"))).view(T, H, 2, dk)
     k, v = kv
     ok, _ = window_mask(T, (m.get("mask") or {}).get("size"))
     lam = torch.exp((t["lq1"] * t["lk1"]).sum()) - torch.exp((t["lq2"] * t["lk2"]).sum()) + m["diff"]
@@ -141,8 +155,8 @@ def differential_attention(h, t, m, eps, kv):
             maps.append(torch.softmax(s, -1) @ v[:, g])
         o = maps[0] - lam * maps[1]
         out[:, head] = rms_normalise(o, eps) * (1 - m["diff"])
-    out = out.reshape(T, H * dv) * torch.sigmoid(h @ t["g"].T)
-    return out @ t["o"].T
+    out = out.reshape(T, H * dv) * torch.sigmoid(stored(h @ t["g"].T))
+    return stored(out) @ t["o"].T
 
 
 # --- matrix memory (mLSTM) ------------------------------------------------------------------------
@@ -152,6 +166,7 @@ def mlstm(h, t, m, eps):
     in range by a running maximum that starts at 0."""
     T = h.shape[0]
     H, dk, dv, cap = m["heads"], m["dim"], m["vdim"], m["gate_cap"]
+    h = stored(h)
     q = (h @ t["q"].T).view(T, H, dk) * dk ** -0.5
     k = (h @ t["k"].T).view(T, H, dk)
     v = (h @ t["v"].T).view(T, H, dv)
@@ -171,7 +186,7 @@ def mlstm(h, t, m, eps):
             below = torch.maximum((n * q[step, head]).sum().abs(), torch.exp(-mx)) + 1e-6
             out[step, head] = (S.T @ q[step, head]) / below
     out = rms_normalise(out, eps).reshape(T, H * dv) * t["norm"] * torch.sigmoid(h @ t["g"].T)
-    return out @ t["o"].T
+    return stored(out) @ t["o"].T
 
 
 # --- the model --------------------------------------------------------------------------------------
@@ -181,9 +196,17 @@ def mixer_tensors(tensors, layer: int, dtype):
     return {k[len(p):]: v.to(dtype) for k, v in tensors.items() if k.startswith(p)}
 
 
-def forward(model, tokens, dtype=torch.float64, layers_out=None):
+def forward(model, tokens, dtype=torch.float64, layers_out=None, rounded=False):
     """Logits [T, vocab] of one whole sequence; ``layers_out`` (a list) receives the residual stream
-    after every layer."""
+    after every layer.  ``rounded``: the rounding variant (see ``stored``)."""
+    ROUND["on"] = bool(rounded)
+    try:
+        return _forward(model, tokens, dtype, layers_out)
+    finally:
+        ROUND["on"] = False
+
+
+def _forward(model, tokens, dtype, layers_out):
     cfg, ts = model["config"], model["tensors"]
     eps = cfg["norm"]["eps"]
     T = len(tokens)
@@ -210,5 +233,5 @@ def forward(model, tokens, dtype=torch.float64, layers_out=None):
             x = x + rms_norm(y, ts[f"l{i}.norm2"].to(dtype), eps)
         if layers_out is not None:
             layers_out.append(x.clone())
-    x = rms_norm(x, ts["final.norm"].to(dtype), eps)
+    x = stored(rms_norm(x, ts["final.norm"].to(dtype), eps))
     return x @ ts["head"].to(dtype).T
