@@ -1,6 +1,7 @@
 """Decode and prefill throughput of the engine at the layer sizes of the LFM2.5 models, random weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--config 8b-a1b|dense-1.2b|dense-2.6b]
+    python bench.py --design beledra        (another design beside dense LFM2 at equal size; one JSON line)
                     [--batch B] [--context C] [--dtype bfloat16|float32] [--impl ours|reference]
 
 Prints ONE JSON line.  Without flags: LFM2.5-8B-A1B sizes, 8 requests at context 8,192.
@@ -37,6 +38,7 @@ import json
 import os
 import pathlib
 import statistics
+import gc
 import subprocess
 import sys
 import tempfile
@@ -73,6 +75,104 @@ CONFIGS = {
     "dense-1.2b": dict(label="LFM2.5-1.2B dense sizes", json=CONFIG_DENSE_1_2B, batch=64, context=32768),
     "dense-2.6b": dict(label="LFM2-2.6B dense sizes", json=CONFIG_DENSE_2_6B, batch=1, context=32768),
 }
+
+
+def _beledra(width: int, layers: int, ff: int, vocab: int = 65536) -> dict:
+    """Beledra at sizes that resemble a real model's layers: every six layers hold three attention layers with a
+    distance bias (window 1,024), a differential attention layer (window 2,048, rotary over the whole head,
+    stretched four times) and a second one that reads the first one's keys and values, and one mLSTM layer
+    without a feed-forward."""
+    heads = width // 64
+    bias = {"type": "attention", "mlp": {"kind": "dense", "ff": ff},
+            "mixer": {"heads": heads, "kv_heads": heads // 4, "dim": 64, "vdim": 64, "scale": 0.125,
+                      "mask": {"size": 1024}, "bias_max": 768, "bias_rows": 32}}
+    diff = {"type": "attention_2", "mlp": {"kind": "dense", "ff": ff},
+            "mixer": {"heads": heads // 2, "kv_heads": heads // 8, "dim": 64, "vdim": 128, "scale": 0.125,
+                      "mask": {"size": 2048}, "diff": 0.5,
+                      "rot": {"dims": 64, "base": 1000000.0,
+                              "scaling": {"factor": 4.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}}
+    memory = {"type": "mlstm", "mlp": None,
+              "mixer": {"heads": heads // 4, "dim": 128, "vdim": 256, "gate_cap": 15.0}}
+    out = []
+    for i in range(layers):
+        kind = i % 6
+        if kind in (0, 1, 5):
+            out.append(json.loads(json.dumps(bias)))
+        elif kind == 2:
+            out.append(json.loads(json.dumps(diff)))
+        elif kind == 3:
+            out.append(json.loads(json.dumps(memory)))
+        else:
+            reader = json.loads(json.dumps(diff))
+            reader["mixer"]["kv_from"] = i - 2
+            out.append(reader)
+    return {"architecture": "Beledra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "layers": out}
+
+
+def _lfm2_like(width: int, layers: int, ff: int, vocab: int = 65536) -> dict:
+    """The closest existing model at equal size: dense LFM2 of the same width, depth, feed-forward width and
+    head counts, an attention layer wherever the other design has one of its attention layers."""
+    heads = width // 64
+    return {"architectures": ["Lfm2ForCausalLM"], "model_type": "lfm2", "vocab_size": vocab, "hidden_size": width,
+            "num_hidden_layers": layers,
+            "layer_types": ["conv" if i % 6 == 3 else "full_attention" for i in range(layers)],
+            "num_attention_heads": heads, "num_key_value_heads": heads // 4, "conv_L_cache": 3, "conv_bias": False,
+            "rope_theta": 1000000.0, "norm_eps": 1e-5, "tie_word_embeddings": True,
+            "max_position_embeddings": 128000, "intermediate_size": ff}
+
+
+DESIGN_SIZES = {"w2048-l12": (2048, 12, 8192), "w1024-l6": (1024, 6, 4096)}
+
+
+def design_compare(a) -> dict:
+    """``--design beledra``: prompt and decode throughput of the Beledra design at DESIGN_SIZES (seeded random
+    weights) beside dense LFM2 at equal size, each with its per-kernel table (time, bytes and flops from the
+    kernels' ledger, the fraction of the measured roofline)."""
+    import torch
+
+    from snowllm_b200.config.engine import DEFAULT_PAGE_SIZE
+    from snowllm_b200.loader import load_random
+    page = a.page_size or DEFAULT_PAGE_SIZE
+    pk, pk_source = peaks()
+    context = a.context or 4096
+    steps, warmup = min(a.steps, 32), max(a.warmup, 3)
+    sampler = ClockSampler(device_id())
+    sampler.start()
+    sizes = {}
+    graphs = not a.enforce_eager
+    for label, (width, layers, ff) in DESIGN_SIZES.items():
+        if a.layers:
+            layers = min(layers, a.layers)
+        models = {who: load_random(cfg, seed=0, dtype=a.dtype, device="cuda")
+                  for who, cfg in (("beledra", _beledra(width, layers, ff)), ("lfm2_dense", _lfm2_like(width, layers, ff)))}
+        torch.cuda.synchronize()
+        per = {who: {} for who in models}
+        # the timed runs first (captured decode steps), the per-kernel tables afterwards, launch by launch:
+        # a capture made after the profiling interface was in use has failed here
+        for who, model in models.items():
+            got = per[who]
+            pms, _ = prefill_run(model, PREFILL_TOKENS, page)
+            got.update(prefill_tok_s=round(PREFILL_TOKENS / (pms / 1e3), 1), prefill_ms=round(pms, 3))
+            for batch in (8, 64):
+                ms, launches, nbytes, _, _ = decode_run(model, batch, context, steps, warmup, page, graphs=graphs)
+                got["decode_b%d_tok_s" % batch] = round(batch / (ms / 1e3), 1)
+                got["decode_b%d_ms" % batch] = round(ms, 4)
+                got["decode_b%d_hbm_frac" % batch] = round(nbytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+                got["decode_b%d_launches_per_step" % batch] = launches // steps
+        for who, model in models.items():
+            _, per[who]["prefill_kernels"] = prefill_run(model, PREFILL_TOKENS, page, repeats=1, report=pk)
+            per[who]["decode_b64_kernels"] = decode_run(model, 64, context, 2, 3, page, graphs=False, report=pk)[4]
+        del models
+        gc.collect()
+        torch.cuda.empty_cache()
+        sizes[label] = dict(width=width, layers=layers, ff=ff, **per)
+    return {"design": "Beledra", "beside": "dense LFM2 at equal width, depth, feed-forward width and head counts",
+            "dtype": a.dtype, "prefill_tokens": PREFILL_TOKENS, "decode_context": context, "page_size": page,
+            "data": "synthetic: seeded random weights and uniform random token ids; cache filled with random values",
+            "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops_sustained": pk["bf16_tflops_sustained"], "of": pk_source},
+            "clocks": sampler.stop(), "sizes": sizes}
+
+
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}
 PREFILL_TOKENS = 2048
 
@@ -383,7 +483,13 @@ def prefill_run(model, tokens: int, page_size: int, chunk: int | None = None, re
         lo, hi = cuts[-1]
 
         def last():                        # the last portion again, over the cache that the portions before left
-            rc.num_tokens = lo
+            nonlocal rc
+            if lo == 0:                    # the whole prompt: a fresh request (a window group has given pages back)
+                cache.free(rc)
+                rc = cache.admit()
+                assert cache.ensure(rc, tokens)
+            else:
+                rc.num_tokens = lo
             runner.step([StepEntry(rc, ids[lo:hi], [hi - lo - 1])])
         whole()
         rows = kernel_report(last, last, 2, report)
@@ -554,6 +660,8 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=None)
     ap.add_argument("--enforce-eager", action="store_true", help="no CUDA graphs for the decode steps")
     ap.add_argument("--skip", default="", help="comma list of: e2e, prefill, points, kernels, mixed")
+    ap.add_argument("--design", default=None, choices=("beledra",),
+                    help="instead of the default workload: this design at a few sizes beside dense LFM2 at equal size")
     a = ap.parse_args()
     if a.impl == "reference":
         print(json.dumps(reference_arm()))
@@ -561,6 +669,9 @@ def main() -> int:
     if a.gpus != 1:
         print("bench.py measures one GPU: this engine does not use more than one (got --gpus %d)" % a.gpus)
         return 2
+    if a.design:
+        print(json.dumps(design_compare(a)))
+        return 0
     warmup = max(a.warmup, 3)
     import torch
 
