@@ -152,7 +152,7 @@ __global__ void split_attention_kernel(
     const int* __restrict__ block_table, int max_pages, int page_size, const int* __restrict__ positions,
     const int* __restrict__ row_seg, const int* __restrict__ tiles, void* __restrict__ out, int out_f32,
     int nq, int nkv, int maps, int dk, int dv, int window, float scale, const float* __restrict__ bias,
-    int bias_len, int vec_ok) {
+    int bias_len, int vec_ok, int chunk, int num_chunks, float* __restrict__ part_o, float* __restrict__ part_ml) {
   pdl_begin();
   extern __shared__ __align__(16) unsigned char sa_raw[];
   constexpr int VEC = SaVec<T>::N;
@@ -163,8 +163,16 @@ __global__ void split_attention_kernel(
   const int hpv = nq / nkv;                              // query heads (maps counted) per kv head
   const int units = rows * hpv;
   const int pos0 = positions[m0];
-  const int lo = window > 0 ? max(0, pos0 - window + 1) : 0;
-  const int hi = pos0 + rows - 1;                        // the last row's own position
+  int lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+  int hi = pos0 + rows - 1;                              // the last row's own position
+  if (num_chunks > 1) {
+    // single rows with their keys cut into chunks aligned to absolute positions: this block takes one
+    // chunk and leaves (o, max, sum) for the merge (attention.cu), which adds the chunks in order
+    const int cnk = lo / chunk + (int)blockIdx.z;
+    if ((long long)cnk * chunk > hi) return;
+    lo = max(lo, cnk * chunk);
+    hi = min(hi, (cnk + 1) * chunk - 1);
+  }
   const int kw = maps * dk;                              // a key row holds the maps side by side
 
   const int k_bytes = kw * (int)sizeof(T), v_bytes = dv * (int)sizeof(T);
@@ -244,9 +252,10 @@ __global__ void split_attention_kernel(
       const int r = u / hpv, hh = u - r * hpv;
       const int map = hh % maps;
       const int p = pos0 + r;
-      const int klo = window > 0 ? max(0, p - window + 1) : 0;
-      if (t0 > p || t0 + SA_TILE - 1 < klo) continue;    // none of this unit's keys in the tile
-      const bool valid = kp >= klo && kp <= p;
+      const int klo = max(lo, window > 0 ? p - window + 1 : 0);
+      const int khi = min(p, hi);
+      if (t0 > khi || t0 + SA_TILE - 1 < klo) continue;  // none of this unit's keys in the tile
+      const bool valid = kp >= klo && kp <= khi;
       const float* qw = qs + (size_t)u * dk;
       float s = 0.f;
       if (vec_ok && dk % VEC == 0) {
@@ -293,6 +302,19 @@ __global__ void split_attention_kernel(
     const int u = warp + nwarps * i;
     if (u >= units) continue;
     const int r = u / hpv, hh = u - r * hpv;
+    if (num_chunks > 1) {
+      const size_t slot = ((size_t)blockIdx.x * nq + kvh * hpv + hh) * num_chunks + blockIdx.z;
+#pragma unroll
+      for (int e = 0; e < DPL; ++e) {
+        const int d = lane + 32 * e;
+        if (d < dv) part_o[slot * dv + d] = o[i][e];
+      }
+      if (lane == 0) {
+        part_ml[slot * 2] = mx[i];
+        part_ml[slot * 2 + 1] = l[i];
+      }
+      continue;
+    }
     const float inv = 1.f / l[i];
     const size_t at = ((size_t)(m0 + r) * nq + kvh * hpv + hh) * dv;
 #pragma unroll
@@ -306,25 +328,365 @@ __global__ void split_attention_kernel(
   }
 }
 
-// Rows a block can serve for `hpv` query heads per kv head: the host cuts its tiles to this.
-SNK_API int snk_split_attention_tile_rows(int hpv, int decode_only) {
-  if (hpv <= 0 || hpv > 32) return 0;
-  return decode_only ? 1 : 32 / hpv;
+// ---------------------------------------------------------------------------------------------
+// The same attention on the tensor cores (bfloat16 only; dk a multiple of 16 up to 16*DKS, dv a multiple of
+// 8 up to 8*DVT, at most 16 query heads per kv head and map).  A warp owns 16 (row, query head) slots of ONE
+// map: they are the rows of mma.sync m16n8k16.  S = Q K^T is exact (bfloat16 products, float sums); scale,
+// bias, mask and the online softmax work on the float fragments; for O += P V the weights are split into two
+// bfloat16 terms, p = hi + lo with lo = bf16(p - hi), and both products are taken, so that P keeps 16
+// mantissa bits where one bfloat16 keeps 8; the row sums use the float weights themselves.
+// Warp w serves map w % maps; its slot s = (w / maps) * 16 + mma row is (row s / G, head s % G of the kv
+// head's G = hpv / maps heads).  All warps of a block read the same key and value tiles.
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+__device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+template <int DKS, int DVT>
+__global__ void split_attention_mma_kernel(
+    const bf16* __restrict__ q, const bf16* __restrict__ kpool, const bf16* __restrict__ vpool,
+    const int* __restrict__ block_table, int max_pages, int page_size, const int* __restrict__ positions,
+    const int* __restrict__ row_seg, const int* __restrict__ tiles, void* __restrict__ out, int out_f32,
+    int nq, int nkv, int maps, int dk, int dv, int window, float scale, const float* __restrict__ bias,
+    int bias_len, int chunk, int num_chunks, float* __restrict__ part_o, float* __restrict__ part_ml) {
+  pdl_begin();
+  extern __shared__ __align__(16) unsigned char sa_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = tiles ? tiles[2 * blockIdx.x] : (int)blockIdx.x;
+  const int rows = tiles ? tiles[2 * blockIdx.x + 1] : 1;
+  const int kvh = blockIdx.y;
+  const int hpv = nq / nkv, G = hpv / maps;
+  const int pos0 = positions[m0];
+  int lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+  int hi = pos0 + rows - 1;
+  if (num_chunks > 1) {
+    const int cnk = lo / chunk + (int)blockIdx.z;
+    if ((long long)cnk * chunk > hi) return;
+    lo = max(lo, cnk * chunk);
+    hi = min(hi, (cnk + 1) * chunk - 1);
+  }
+  const int kw = maps * dk;
+  const float scale2 = scale * 1.4426950408889634f;
+  const int k_bytes = kw * 2, v_bytes = dv * 2;
+  const int k_stride = k_bytes + 16, v_stride = v_bytes + 16;
+  const int stage_bytes = SA_TILE * (k_stride + v_stride);
+
+  // this warp's map and its two rows' slots (mma rows lane/4 and lane/4 + 8)
+  const int map = warp % maps;
+  const int quad = lane >> 2, tq = lane & 3;
+  const int slots = rows * G;
+  int p_row[2], head[2];
+  bool live[2];
+#pragma unroll
+  for (int h2 = 0; h2 < 2; ++h2) {
+    const int s = (warp / maps) * 16 + quad + 8 * h2;
+    live[h2] = s < slots;
+    const int r = live[h2] ? s / G : 0;
+    p_row[h2] = pos0 + r;
+    head[h2] = kvh * hpv + (live[h2] ? (s % G) : 0) * maps + map;
+  }
+  const bool warp_live = (warp / maps) * 16 < slots;
+
+  // Q fragments straight from global memory: a0 (row A, d 2tq..), a1 (row B), a2 (row A, d + 8), a3 (row B, d + 8)
+  uint32_t qa[DKS][4];
+#pragma unroll
+  for (int ks = 0; ks < DKS; ++ks) {
+#pragma unroll
+    for (int h2 = 0; h2 < 2; ++h2) {
+      uint32_t x0 = 0, x1 = 0;
+      if (live[h2] && ks * 16 < dk) {
+        const bf16* qr = q + ((size_t)(m0 + (p_row[h2] - pos0)) * nq + head[h2]) * dk + ks * 16 + tq * 2;
+        x0 = *reinterpret_cast<const uint32_t*>(qr);
+        x1 = *reinterpret_cast<const uint32_t*>(qr + 8);
+      }
+      qa[ks][h2] = x0;
+      qa[ks][2 + h2] = x1;
+    }
+  }
+
+  const int* bt = block_table + (size_t)row_seg[m0] * max_pages;
+  const int t_first = (lo / SA_TILE) * SA_TILE;
+  const int ntiles = (hi - t_first) / SA_TILE + 1;
+  // which (key of the tile, 16-byte vector of its row) pairs this thread copies: the same for every tile
+  const int kv_ = k_bytes / 16, vv_ = v_bytes / 16, per = kv_ + vv_;
+  constexpr int COPIES = 6;                                // 32 keys x up to 48 vectors over 32..128 threads
+  int cp_j[COPIES], cp_c[COPIES];
+  const int n_copies = (SA_TILE * per + (int)blockDim.x - 1) / (int)blockDim.x;
+#pragma unroll
+  for (int i = 0; i < COPIES; ++i) {
+    const int v = threadIdx.x + i * blockDim.x;
+    cp_j[i] = v < SA_TILE * per ? v / per : -1;
+    cp_c[i] = v - (v / per) * per;
+  }
+  const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
+  auto copy_one = [&](unsigned char* ks_, unsigned char* vs_, int t0, int j, int c) {
+    const int kp = t0 + j;
+    const bool valid = kp >= lo && kp <= hi;
+    const bf16* src = kpool;
+    unsigned char* dst = c < kv_ ? ks_ + j * k_stride + c * 16 : vs_ + j * v_stride + (c - kv_) * 16;
+    if (valid) {
+      const int pg = page_shift >= 0 ? kp >> page_shift : kp / page_size;
+      const size_t slot = ((size_t)bt[pg] * nkv + kvh) * page_size + (kp - pg * page_size);
+      src = c < kv_ ? kpool + slot * kw + c * 8 : vpool + slot * dv + (c - kv_) * 8;
+    }
+    sa_cp_async16(dst, src, valid);
+  };
+  auto issue = [&](int tile) {
+    if (tile < ntiles) {
+      const int t0 = t_first + tile * SA_TILE;
+      unsigned char* ks_ = sa_raw + (size_t)(tile % SA_STAGES) * stage_bytes;
+      unsigned char* vs_ = ks_ + SA_TILE * k_stride;
+#pragma unroll
+      for (int i = 0; i < COPIES; ++i)
+        if (cp_j[i] >= 0) copy_one(ks_, vs_, t0, cp_j[i], cp_c[i]);
+      for (int i = COPIES; i < n_copies; ++i) {            // few threads and wide rows: the rest the long way
+        const int v = threadIdx.x + i * blockDim.x;
+        if (v < SA_TILE * per) copy_one(ks_, vs_, t0, v / per, v - (v / per) * per);
+      }
+    }
+    sa_cp_async_commit();
+  };
+
+  float mx[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+  float o[DVT][4];
+#pragma unroll
+  for (int nt = 0; nt < DVT; ++nt)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[nt][e] = 0.f;
+  int klo[2], khi[2];
+#pragma unroll
+  for (int h2 = 0; h2 < 2; ++h2) {
+    klo[h2] = max(lo, window > 0 ? p_row[h2] - window + 1 : 0);
+    khi[h2] = live[h2] ? min(p_row[h2], hi) : -1;           // a slot nobody owns sees no key
+  }
+
+#pragma unroll
+  for (int s = 0; s < SA_STAGES - 1; ++s) issue(s);
+  for (int tile = 0; tile < ntiles; ++tile) {
+    sa_cp_async_wait<SA_STAGES - 2>();
+    __syncthreads();
+    issue(tile + SA_STAGES - 1);
+    const int t0 = t_first + tile * SA_TILE;
+    // the warp's slots span positions pos0 + first slot / G .. ; skip tiles none of them reaches
+    if (!warp_live) continue;
+    {
+      const int s_lo = (warp / maps) * 16, s_hi = min(slots - 1, s_lo + 15);
+      const int p_lo = pos0 + s_lo / G, p_hi = pos0 + s_hi / G;
+      const int w_lo = max(lo, window > 0 ? p_lo - window + 1 : 0), w_hi = min(p_hi, hi);
+      if (t0 > w_hi || t0 + SA_TILE - 1 < w_lo) continue;
+    }
+    const unsigned char* ks_ = sa_raw + (size_t)(tile % SA_STAGES) * stage_bytes;
+    const unsigned char* vs_ = ks_ + SA_TILE * k_stride;
+    // S = Q K^T: 4 tiles of 8 keys
+    float sc[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+      sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+      const unsigned char* kr = ks_ + (nt * 8 + quad) * k_stride + (map * dk + tq * 2) * 2;
+#pragma unroll
+      for (int ks = 0; ks < DKS; ++ks) {
+        if (ks * 16 < dk) {
+          const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kr + ks * 32);
+          const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kr + ks * 32 + 16);
+          mma_bf16_16816(sc[nt], qa[ks], b0, b1);
+        }
+      }
+    }
+    // scale, bias, mask; row maxima over the thread's 8 keys, then over the quad
+    // (scores and maxima are kept in units of log 2: the weights are 2^(s - m), one instruction each)
+    float tmax[2] = {-INFINITY, -INFINITY};
+    const bool inner = t0 >= max(klo[0], klo[1]) && t0 + SA_TILE - 1 <= min(khi[0], khi[1]);   // no key is masked
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int h2 = e >> 1;
+        const int kp = t0 + nt * 8 + tq * 2 + (e & 1);
+        float s = sc[nt][e] * scale2;
+        const bool valid = inner || (kp >= klo[h2] && kp <= khi[h2]);
+        if (bias && valid)
+          s = fmaf(bias[(size_t)head[h2] * bias_len + min(p_row[h2] - kp, bias_len - 1)], 1.4426950408889634f, s);
+        s = valid ? s : -INFINITY;
+        sc[nt][e] = s;
+        tmax[h2] = fmaxf(tmax[h2], s);
+      }
+    }
+    float corr[2];
+#pragma unroll
+    for (int h2 = 0; h2 < 2; ++h2) {
+      tmax[h2] = fmaxf(tmax[h2], __shfl_xor_sync(0xffffffffu, tmax[h2], 1));
+      tmax[h2] = fmaxf(tmax[h2], __shfl_xor_sync(0xffffffffu, tmax[h2], 2));
+      const float m_new = fmaxf(mx[h2], tmax[h2]);
+      // a row without a key so far keeps -inf: its weights are 0 and its correction 1
+      corr[h2] = m_new == -INFINITY ? 1.f : exp2f(mx[h2] - m_new);
+      mx[h2] = m_new;
+    }
+    float psum[2] = {0.f, 0.f};
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int h2 = e >> 1;
+        const float pw = sc[nt][e] == -INFINITY ? 0.f : exp2f(sc[nt][e] - mx[h2]);
+        sc[nt][e] = pw;
+        psum[h2] += pw;
+      }
+    }
+#pragma unroll
+    for (int h2 = 0; h2 < 2; ++h2) {
+      psum[h2] += __shfl_xor_sync(0xffffffffu, psum[h2], 1);
+      psum[h2] += __shfl_xor_sync(0xffffffffu, psum[h2], 2);
+      l[h2] = l[h2] * corr[h2] + psum[h2];
+    }
+#pragma unroll
+    for (int nt = 0; nt < DVT; ++nt) {
+      o[nt][0] *= corr[0]; o[nt][1] *= corr[0];
+      o[nt][2] *= corr[1]; o[nt][3] *= corr[1];
+    }
+    // O += P V in two bfloat16 terms of P; 16 keys per step
+#pragma unroll
+    for (int kt = 0; kt < 2; ++kt) {
+      uint32_t ph[4], pl[4];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const float* c = sc[2 * kt + half];
+        const float h0 = bf16_round(c[0]), h1 = bf16_round(c[1]), h2_ = bf16_round(c[2]), h3 = bf16_round(c[3]);
+        ph[2 * half] = pack_bf16(h0, h1);
+        ph[2 * half + 1] = pack_bf16(h2_, h3);
+        pl[2 * half] = pack_bf16(c[0] - h0, c[1] - h1);
+        pl[2 * half + 1] = pack_bf16(c[2] - h2_, c[3] - h3);
+      }
+      const unsigned char* vr = vs_ + (kt * 16 + tq * 2) * v_stride + quad * 2;
+#pragma unroll
+      for (int nt = 0; nt < DVT; ++nt) {
+        if (nt * 8 < dv) {
+          const unsigned char* vp = vr + nt * 16;
+          const uint32_t b0 = (uint32_t)*reinterpret_cast<const unsigned short*>(vp) |
+                              ((uint32_t)*reinterpret_cast<const unsigned short*>(vp + v_stride) << 16);
+          const uint32_t b1 = (uint32_t)*reinterpret_cast<const unsigned short*>(vp + 8 * v_stride) |
+                              ((uint32_t)*reinterpret_cast<const unsigned short*>(vp + 9 * v_stride) << 16);
+          mma_bf16_16816(o[nt], ph, b0, b1);
+          mma_bf16_16816(o[nt], pl, b0, b1);
+        }
+      }
+    }
+  }
+  sa_cp_async_wait<0>();
+#pragma unroll
+  for (int h2 = 0; h2 < 2; ++h2) {
+    if (!live[h2]) continue;
+    const int r = p_row[h2] - pos0;
+    if (num_chunks > 1) {
+      const size_t slot = ((size_t)blockIdx.x * nq + head[h2]) * num_chunks + blockIdx.z;
+#pragma unroll
+      for (int nt = 0; nt < DVT; ++nt) {
+        const int d = nt * 8 + tq * 2;
+        if (d < dv) {
+          part_o[slot * dv + d] = o[nt][2 * h2];
+          part_o[slot * dv + d + 1] = o[nt][2 * h2 + 1];
+        }
+      }
+      if (tq == 0) {
+        part_ml[slot * 2] = mx[h2] * 0.6931471805599453f;    // the merge works with natural exponents
+        part_ml[slot * 2 + 1] = l[h2];
+      }
+      continue;
+    }
+    const float inv = 1.f / l[h2];
+    const size_t at = ((size_t)(m0 + r) * nq + head[h2]) * dv;
+#pragma unroll
+    for (int nt = 0; nt < DVT; ++nt) {
+      const int d = nt * 8 + tq * 2;
+      if (d < dv) {
+        const float a = o[nt][2 * h2] * inv, b = o[nt][2 * h2 + 1] * inv;
+        if (out_f32) {
+          static_cast<float*>(out)[at + d] = a;
+          static_cast<float*>(out)[at + d + 1] = b;
+        } else {
+          *reinterpret_cast<uint32_t*>(static_cast<bf16*>(out) + at + d) = pack_bf16(a, b);
+        }
+      }
+    }
+  }
+}
+
+// Whether the tensor-core kernel takes these sizes.
+static bool sa_mma_ok(int dtype, int nq, int nkv, int maps, int dk, int dv) {
+  if (dtype != SNK_BF16 || nkv <= 0 || maps <= 0 || maps > 4 || nq % (nkv * maps)) return false;
+  const int G = nq / nkv / maps;
+  return G <= 16 && dk % 16 == 0 && dk <= 128 && dv % 8 == 0 && dv <= 128;
+}
+
+// Rows of one request that a block serves: the host cuts its tiles to this.  `dk`, `dv`, `dtype`: with sizes
+// the tensor-core kernel takes, a block of four warps holds 64 / maps slots per map.  0: sizes nobody takes.
+SNK_API int snk_split_attention_tile_rows(int nq, int nkv, int maps, int dk, int dv, int dtype, int decode_only) {
+  if (nkv <= 0 || maps <= 0 || nq % (nkv * maps)) return 0;
+  const int hpv = nq / nkv;
+  if (decode_only) return sa_mma_ok(dtype, nq, nkv, maps, dk, dv) || hpv <= 32 ? 1 : 0;
+  if (sa_mma_ok(dtype, nq, nkv, maps, dk, dv)) {
+    const int per_map = 16 * (4 / maps), G = hpv / maps;
+    return per_map / G;
+  }
+  return hpv <= 32 ? 32 / hpv : 0;
 }
 
 // tiles: int32 [num_tiles, 2] = (first row, rows <= tile_rows), consecutive rows of one request; null:
-// num_tiles rows, one per block.
+// num_tiles rows, one per block.  num_chunks > 1 (single rows only): each row's keys in chunks of `chunk`
+// (a multiple of 32) with partial results in `scratch`, laid out as snk_attention_merge (attention.cu)
+// reads them; the caller runs that merge next.
 SNK_API int snk_split_attention(const void* q, const void* kpool, const void* vpool, const int* block_table,
                                 int max_pages, int page_size, const int* positions, const int* row_seg,
                                 const int* tiles, int num_tiles, int tile_rows, void* out, int out_f32, int nq,
                                 int nkv, int maps, int dk, int dv, int window, float scale, const float* bias,
-                                int bias_len, int dtype, cudaStream_t stream) {
+                                int bias_len, int chunk, int num_chunks, void* scratch, int dtype,
+                                cudaStream_t stream) {
   if (num_tiles <= 0) return 0;
   if (nkv <= 0 || maps <= 0 || nq % (nkv * maps) || dk <= 0 || dv <= 0 || dv > 256) return SNK_ERR_SIZE;
   const int hpv = nq / nkv;
-  if (hpv > 32 || tile_rows < 1 || tile_rows * hpv > 32 || nkv > 65535) return SNK_ERR_SIZE;
+  if (tile_rows < 1 || nkv > 65535) return SNK_ERR_SIZE;
   if (!tiles) tile_rows = 1;
   if (bias && bias_len <= 0) return SNK_ERR_SIZE;
+  if (num_chunks < 1 || num_chunks > 65535) return SNK_ERR_SIZE;
+  if (num_chunks > 1 && (tiles || scratch == nullptr || chunk <= 0 || chunk % SA_TILE)) return SNK_ERR_SIZE;
+  float* part_o = static_cast<float*>(scratch);
+  float* part_ml = part_o ? part_o + (size_t)num_tiles * nq * num_chunks * dv : nullptr;
+  // rows that stand alone (decoded tokens) stay on the CUDA-core kernel: 16-row tiles with one row in use
+  // were measured slower there (1,363 against 905 us for 64 rows over windows of 2,048)
+  if (tiles && sa_mma_ok(dtype, nq, nkv, maps, dk, dv) && (uintptr_t)kpool % 16 == 0 &&
+      (uintptr_t)vpool % 16 == 0 && (uintptr_t)q % 4 == 0) {
+    const int G = hpv / maps;
+    const int slots = tile_rows * G;                       // per map
+    if (slots > 16 * (4 / maps)) return SNK_ERR_SIZE;
+    const int warps = maps * ((slots + 15) / 16);
+    const size_t stage = (size_t)SA_TILE * ((size_t)maps * dk * 2 + 16 + (size_t)dv * 2 + 16);
+    const size_t smem = SA_STAGES * stage;
+    if (smem > 227 * 1024) return SNK_ERR_SIZE;
+    dim3 grid(num_tiles, nkv, num_chunks);
+#define SA_MMA(DKS_, DVT_)                                                                                   \
+  do {                                                                                                       \
+    if (smem > 48 * 1024)                                                                                    \
+      cudaFuncSetAttribute(split_attention_mma_kernel<DKS_, DVT_>,                                           \
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                          \
+    snk_launch(split_attention_mma_kernel<DKS_, DVT_>, dim3(grid), dim3(warps * 32), smem, stream,           \
+               static_cast<const bf16*>(q), static_cast<const bf16*>(kpool), static_cast<const bf16*>(vpool), \
+               block_table, max_pages, page_size, positions, row_seg, tiles, out, out_f32, nq, nkv, maps,    \
+               dk, dv, window, scale, bias, bias_len, chunk, num_chunks, part_o, part_ml);                   \
+  } while (0)
+    if (dk <= 64 && dv <= 64) SA_MMA(4, 8);
+    else if (dk <= 64) SA_MMA(4, 16);
+    else if (dv <= 64) SA_MMA(8, 8);
+    else SA_MMA(8, 16);
+#undef SA_MMA
+    SNK_LAUNCH_CHECK();
+    return 0;
+  }
+  if (hpv > 32 || tile_rows * hpv > 32) return SNK_ERR_SIZE;
   const int esz = dtype == SNK_F32 ? 4 : 2;
   const int kw = maps * dk;
   const int vec_ok = (kw * esz) % 16 == 0 && (dv * esz) % 16 == 0 && (uintptr_t)kpool % 16 == 0 &&
@@ -335,7 +697,7 @@ SNK_API int snk_split_attention(const void* q, const void* kpool, const void* vp
   const size_t stage = (size_t)SA_TILE * ((((size_t)kw * esz + 15) & ~(size_t)15) + 16 + (((size_t)dv * esz + 15) & ~(size_t)15) + 16);
   const size_t smem = SA_STAGES * stage + (size_t)cap * dk * sizeof(float);
   if (smem > 227 * 1024) return SNK_ERR_SIZE;
-  dim3 grid(num_tiles, nkv);
+  dim3 grid(num_tiles, nkv, num_chunks);
 #define SA_LAUNCH(DPL_, UPW_)                                                                          \
   do {                                                                                                 \
     if (smem > 48 * 1024)                                                                              \
@@ -344,7 +706,7 @@ SNK_API int snk_split_attention(const void* q, const void* kpool, const void* vp
     snk_launch(split_attention_kernel<T, DPL_, UPW_>, dim3(grid), dim3(warps * 32), smem, stream,      \
                static_cast<const T*>(q), static_cast<const T*>(kpool), static_cast<const T*>(vpool),   \
                block_table, max_pages, page_size, positions, row_seg, tiles, out, out_f32, nq, nkv,    \
-               maps, dk, dv, window, scale, bias, bias_len, vec_ok);                                   \
+               maps, dk, dv, window, scale, bias, bias_len, vec_ok, chunk, num_chunks, part_o, part_ml); \
   } while (0)
 #define SA_LAUNCH_U(DPL_)                  \
   do {                                     \

@@ -88,8 +88,8 @@ _SIGNATURES = {
     },
     "attention_split": {
         "snk_split_prepare": [P, LL, I, I, I, P, P, I, I, F, P, I, F, P, P, P, I, I, P, P, P, I, I, I, I, I, I, I, I, P],
-        "snk_split_attention_tile_rows": [I, I],
-        "snk_split_attention": [P, P, P, P, I, I, P, P, P, I, I, P, I, I, I, I, I, I, I, F, P, I, I, P],
+        "snk_split_attention_tile_rows": [I, I, I, I, I, I, I],
+        "snk_split_attention": [P, P, P, P, I, I, P, P, P, I, I, P, I, I, I, I, I, I, I, F, P, I, I, I, P, I, P],
     },
     "mlstm": {
         "snk_mlstm": [P, LL, I, I, I, I, I, P, P, I, F, P, P, P, P, P, P, P, I, I, I, I, P],
@@ -1172,19 +1172,28 @@ def split_prepare(proj, q_off, k_off, v_off, q_gamma, k_gamma, eps, inv_freq, ro
     return q_out
 
 
-def split_attention_tile_rows(heads_per_kv: int, decode_only: bool) -> int:
-    """Rows of one request that a block of ``split_attention`` serves (0: too many heads per kv head)."""
-    return int(fn("snk_split_attention_tile_rows")(int(heads_per_kv), int(decode_only)))
+def split_attention_tile_rows(nq: int, nkv: int, maps: int, dk: int, dv: int, dtype, decode_only: bool) -> int:
+    """Rows of one request that a block of ``split_attention`` serves for these sizes (0: too many heads per
+    kv head).  bfloat16 with dk a multiple of 16 and dv a multiple of 8, both up to 128, runs on the tensor
+    cores; everything else on the CUDA cores."""
+    return int(fn("snk_split_attention_tile_rows")(int(nq), int(nkv), int(maps), int(dk), int(dv), code_of(dtype),
+                                                   int(decode_only)))
+
+
+SPLIT_ATTENTION_CHUNK = 256
 
 
 def split_attention(q, kpool, vpool, block_table, page_size, positions, row_seg, scale, *, maps=1, window=None,
-                    bias=None, tiles=None, tile_rows=1, out_dtype=None, out=None):
+                    bias=None, tiles=None, tile_rows=1, out_dtype=None, out=None, num_chunks=1, scratch=None):
     """Causal attention of q [M, nq, dk] (nq = heads * maps) over keys [pages, nkv, page_size, maps*dk] and
     values [pages, nkv, page_size, dv]; query head (h, map) reads the key at offset map*dk of its kv head.
     ``window``: the last ``window`` keys only.  ``bias`` float [nq, L]: added to the scaled score by
     distance min(i - j, L - 1).  ``tiles`` int32 [n, 2] = (first row, rows <= tile_rows) of consecutive
-    rows of one request, covering the step; None: every row alone.  Scores, weights and sums are float;
-    returns [M, nq, dv] in ``out_dtype`` (float32 or the compute dtype)."""
+    rows of one request, covering the step; None: every row alone.  ``num_chunks`` > 1 (rows alone only):
+    a row's keys are cut into chunks of SPLIT_ATTENTION_CHUNK at absolute positions, one block each, and
+    merged in chunk order (``num_chunks``: the most chunks a row spans; needs ``scratch`` bytes as
+    ``attention_scratch_bytes`` says).  Scores, weights and sums are float; returns [M, nq, dv] in
+    ``out_dtype`` (float32 or the compute dtype)."""
     M, nq, dk = q.shape
     dtype = q.dtype
     _chk(q, "q", (torch.float32, torch.bfloat16))
@@ -1213,6 +1222,16 @@ def split_attention(q, kpool, vpool, block_table, page_size, positions, row_seg,
     if out is None:
         out = torch.empty(M, nq, dv, dtype=out_dtype, device=q.device)
     _chk(out, "attention output", out_dtype, (M, nq, dv))
+    num_chunks = int(num_chunks)
+    if num_chunks > 1:
+        if tiles is not None:
+            raise KernelError("keys are cut into chunks for rows that stand alone only")
+        need = attention_scratch_bytes(M, nq, dv, num_chunks)
+        if scratch is None:
+            scratch = torch.empty(need, dtype=torch.uint8, device=q.device)
+        _chk(scratch, "attention scratch", torch.uint8)
+        if scratch.numel() < need:
+            raise KernelError(f"attention scratch holds {scratch.numel()} bytes, needs {need}")
 
     def work():
         pos = positions.cpu().long()
@@ -1224,7 +1243,12 @@ def split_attention(q, kpool, vpool, block_table, page_size, positions, row_seg,
         _ptr(q), _ptr(kpool), _ptr(vpool), _ptr(block_table), block_table.shape[1], page_size, _ptr(positions),
         _ptr(row_seg), _ptr(tiles), n_tiles, int(tile_rows), _ptr(out), int(out_dtype == torch.float32 and dtype != torch.float32),
         nq, nkv, int(maps), dk, dv, int(window or 0), float(scale), _ptr(bias),
-        bias.shape[1] if bias is not None else 0, code_of(dtype), _stream()), "split_attention", work=work)
+        bias.shape[1] if bias is not None else 0, SPLIT_ATTENTION_CHUNK, num_chunks, _ptr(scratch),
+        code_of(dtype), _stream()), "split_attention", work=work)
+    if num_chunks > 1:
+        check(fn("snk_attention_merge")(_ptr(scratch), _ptr(positions), _ptr(out), M, nq, dv, int(window or 0),
+                                        SPLIT_ATTENTION_CHUNK, num_chunks, code_of(out_dtype), c_void_p(0), _stream()),
+              "attention_merge", work=lambda: (M * nq * (dv + 2) * 4 * num_chunks + _nbytes(out), 0))
     return out
 
 

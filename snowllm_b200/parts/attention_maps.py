@@ -26,6 +26,7 @@ import torch
 
 from ..errors import ConfigError, KernelError
 from ..ops import kernels, linear
+from . import attention_plan as plan
 from .base import Part
 from .registry import lookup, register_mixer
 from .spec import INIT_ONES, KEEP_F32, KEEP_SMALL, PagedKVSpec, TensorSpec
@@ -88,7 +89,7 @@ def attention_tiles(ctx, tile_rows: int):
 
 
 class MapsAttention(Part):
-    libraries = ("gemm", "gemm_skinny", "gemm_tc", "gemm_tc2", "attention_split", "sublayer")
+    libraries = ("gemm", "gemm_skinny", "gemm_tc", "gemm_tc2", "attention_split", "attention", "sublayer")
     maps = 1
 
     def __init__(self, dtype, names, *, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
@@ -176,11 +177,20 @@ class MapsAttention(Part):
                                   write_kv=owns_cache)
         ctx.tap("attention_q", q)
         decode_only = max(ctx.host_seg_len) <= 1
-        tile_rows = kernels.split_attention_tile_rows(self.nq // self.num_kv_heads, decode_only)
+        tile_rows = kernels.split_attention_tile_rows(self.nq, self.num_kv_heads, self.maps, self.head_dim,
+                                                      self.v_head_dim, self.dtype, decode_only)
+        num_chunks, scratch = 1, None
+        if decode_only:
+            # rows of decoded tokens: their keys in chunks of 256, one block each, merged in chunk order
+            num_chunks = plan.chunks(ctx, self.window, None, kernels.SPLIT_ATTENTION_CHUNK)
+            if self.window:                # a captured step plans for its longest sequence; a window spans fewer
+                num_chunks = min(num_chunks, (self.window - 1) // kernels.SPLIT_ATTENTION_CHUNK + 2)
+            if num_chunks > 1:
+                scratch = ctx.scratch(kernels.attention_scratch_bytes(ctx.M, self.nq, self.v_head_dim, num_chunks))
         out = kernels.split_attention(q, kpool, vpool, cache.block_table, cache.page_size, ctx.positions,
                                       ctx.row_seg, self.scale, maps=self.maps, window=self.window, bias=self.bias,
                                       tiles=attention_tiles(ctx, tile_rows), tile_rows=tile_rows,
-                                      out_dtype=out_dtype)
+                                      out_dtype=out_dtype, num_chunks=num_chunks, scratch=scratch)
         ctx.tap("attention_o", out)
         return proj, out
 

@@ -122,7 +122,7 @@ def test_attention_kernel_sees_exactly_its_window(dtype, tiled):
     table = order.view(1, -1).cuda().contiguous()
     tiles, tile_rows = None, 1
     if tiled:
-        tile_rows = kernels.split_attention_tile_rows(H, False)
+        tile_rows = kernels.split_attention_tile_rows(H, 1, 1, dk, dv, dtype, False)
         starts = list(range(0, T, tile_rows))
         tiles = torch.tensor([[s, min(tile_rows, T - s)] for s in starts], dtype=torch.int32, device="cuda")
     got = kernels.split_attention(q.cuda(), kpool, vpool, table, P, positions, row_seg, 0.25, window=window,
