@@ -181,3 +181,15 @@ def test_plain_implementation_is_causal_and_respects_each_window():
     other[39 - (9 - 1) - (7 - 1)] = (other[39 - 14] + 1) % cfg["vocab"]         # the farthest token that can matter
     assert not torch.equal(cases.plain_logits(cfg, tensors, other)[-1], base[-1])
     assert torch.equal(cases.plain_logits(cfg, tensors, toks[:25]), base[:25])  # causal
+
+
+def test_bench_design_option_builds_both_models_at_equal_size():
+    import bench
+    for width, layers, ff in bench.DESIGN_SIZES.values():
+        ours = build_model(bench._beledra(width, layers, ff), "bfloat16")
+        theirs = build_model(bench._lfm2_like(width, layers, ff), "bfloat16")
+        assert len(ours.run) == len(theirs.run) == layers
+        assert ours.spec.hidden_size == theirs.spec.hidden_size == width
+        kinds = [type(b.mixer).__name__ for b in ours.blocks]
+        assert {"BiasAttention", "DiffAttention", "MLstm"} == set(kinds)
+        assert any(e.cache_of is not None for e in ours.run)
