@@ -616,6 +616,225 @@ __global__ void split_attention_mma_kernel(
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Rows that stand alone (decoded tokens) on the tensor cores.  A block takes one row, one kv head and one
+// chunk of SD_CHUNK keys at absolute positions; the whole chunk comes into shared memory at once (every copy
+// in flight together), then each of the four warps takes 32 of its keys with the kv head's G query heads on
+// the rows of the MMA (one map after the other), and the warps' partial (max, sum, o) are merged in warp
+// order through shared memory.  More than one chunk: the block leaves its partial for the merge kernel.
+#define SD_CHUNK 128
+#define SD_WARPS 4
+
+template <int DKS, int DVT>
+__global__ void __launch_bounds__(SD_WARPS * 32)
+split_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kpool, const bf16* __restrict__ vpool,
+                        const int* __restrict__ block_table, int max_pages, int page_size,
+                        const int* __restrict__ positions, const int* __restrict__ row_seg,
+                        void* __restrict__ out, int out_f32, int nq, int nkv, int maps, int dk, int dv, int window,
+                        float scale, const float* __restrict__ bias, int bias_len, int num_chunks,
+                        float* __restrict__ part_o, float* __restrict__ part_ml) {
+  pdl_begin();
+  extern __shared__ __align__(16) unsigned char sa_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int quad = lane >> 2, tq = lane & 3;
+  const int m = blockIdx.x, kvh = blockIdx.y;
+  const int hpv = nq / nkv, G = hpv / maps;
+  const int pos = positions[m];
+  const int lo_row = window > 0 ? max(0, pos - window + 1) : 0;
+  const int cnk = lo_row / SD_CHUNK + (int)blockIdx.z;
+  if ((long long)cnk * SD_CHUNK > pos) return;
+  const int c0 = cnk * SD_CHUNK;
+  const int lo = max(lo_row, c0), hi = min(pos, c0 + SD_CHUNK - 1);
+  const int kw = maps * dk;
+  const float scale2 = scale * 1.4426950408889634f;
+  const int k_bytes = kw * 2, v_bytes = dv * 2;
+  const int k_stride = k_bytes + 16, v_stride = v_bytes + 16;
+  unsigned char* ks_all = sa_raw;
+  unsigned char* vs_all = sa_raw + (size_t)SD_CHUNK * k_stride;
+  float* red = reinterpret_cast<float*>(sa_raw + (size_t)SD_CHUNK * (k_stride + v_stride));   // [maps][G][warps][dv + 2]
+  const int red_stride = dv + 2;
+
+  {
+    const int* bt = block_table + (size_t)row_seg[m] * max_pages;
+    const int kv_ = k_bytes / 16, vv_ = v_bytes / 16, per = kv_ + vv_;
+    // shifts where the sizes are powers of two (the usual case): the copy loop is then free of divisions
+    const int per_shift = (per & (per - 1)) == 0 ? __ffs(per) - 1 : -1;
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
+    for (int v = threadIdx.x; v < SD_CHUNK * per; v += blockDim.x) {
+      const int j = per_shift >= 0 ? v >> per_shift : v / per, c = v - j * per;
+      const int kp = c0 + j;
+      const bool valid = kp >= lo && kp <= hi;
+      const bf16* src = kpool;
+      unsigned char* dst = c < kv_ ? ks_all + j * k_stride + c * 16 : vs_all + j * v_stride + (c - kv_) * 16;
+      if (valid) {
+        const int pg = page_shift >= 0 ? kp >> page_shift : kp / page_size;
+        const size_t slot = ((size_t)bt[pg] * nkv + kvh) * page_size + (kp - pg * page_size);
+        src = c < kv_ ? kpool + slot * kw + c * 8 : vpool + slot * dv + (c - kv_) * 8;
+      }
+      sa_cp_async16(dst, src, valid);
+    }
+    sa_cp_async_commit();
+    sa_cp_async_wait<0>();
+  }
+  __syncthreads();
+
+  const int t0 = c0 + warp * SA_TILE;
+  const bool warp_has = t0 <= hi && t0 + SA_TILE - 1 >= lo;
+  const unsigned char* ks_ = ks_all + (size_t)warp * SA_TILE * k_stride;
+  const unsigned char* vs_ = vs_all + (size_t)warp * SA_TILE * v_stride;
+  const bool live[2] = {quad < G, quad + 8 < G};
+  for (int map = 0; map < maps; ++map) {
+    float mrow[2] = {-INFINITY, -INFINITY}, lrow[2] = {0.f, 0.f};
+    float o[DVT][4];
+#pragma unroll
+    for (int nt = 0; nt < DVT; ++nt) o[nt][0] = o[nt][1] = o[nt][2] = o[nt][3] = 0.f;
+    if (warp_has) {
+      int head[2];
+      uint32_t qa[DKS][4];
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) head[h2] = kvh * hpv + (live[h2] ? quad + 8 * h2 : 0) * maps + map;
+#pragma unroll
+      for (int ks = 0; ks < DKS; ++ks) {
+#pragma unroll
+        for (int h2 = 0; h2 < 2; ++h2) {
+          uint32_t x0 = 0, x1 = 0;
+          if (live[h2] && ks * 16 < dk) {
+            const bf16* qr = q + ((size_t)m * nq + head[h2]) * dk + ks * 16 + tq * 2;
+            x0 = *reinterpret_cast<const uint32_t*>(qr);
+            x1 = *reinterpret_cast<const uint32_t*>(qr + 8);
+          }
+          qa[ks][h2] = x0;
+          qa[ks][2 + h2] = x1;
+        }
+      }
+      float sc[4][4];
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+        sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+        const unsigned char* kr = ks_ + (nt * 8 + quad) * k_stride + (map * dk + tq * 2) * 2;
+#pragma unroll
+        for (int ks = 0; ks < DKS; ++ks) {
+          if (ks * 16 < dk) {
+            const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kr + ks * 32);
+            const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kr + ks * 32 + 16);
+            mma_bf16_16816(sc[nt], qa[ks], b0, b1);
+          }
+        }
+      }
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int h2 = e >> 1;
+          const int kp = t0 + nt * 8 + tq * 2 + (e & 1);
+          float sv = sc[nt][e] * scale2;
+          const bool valid = live[h2] && kp >= lo && kp <= hi;
+          if (bias && valid)
+            sv = fmaf(bias[(size_t)head[h2] * bias_len + min(pos - kp, bias_len - 1)], 1.4426950408889634f, sv);
+          sv = valid ? sv : -INFINITY;
+          sc[nt][e] = sv;
+          mrow[h2] = fmaxf(mrow[h2], sv);
+        }
+      }
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        mrow[h2] = fmaxf(mrow[h2], __shfl_xor_sync(0xffffffffu, mrow[h2], 1));
+        mrow[h2] = fmaxf(mrow[h2], __shfl_xor_sync(0xffffffffu, mrow[h2], 2));
+      }
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int h2 = e >> 1;
+          const float pw = sc[nt][e] == -INFINITY ? 0.f : exp2f(sc[nt][e] - mrow[h2]);
+          sc[nt][e] = pw;
+          lrow[h2] += pw;
+        }
+      }
+#pragma unroll
+      for (int h2 = 0; h2 < 2; ++h2) {
+        lrow[h2] += __shfl_xor_sync(0xffffffffu, lrow[h2], 1);
+        lrow[h2] += __shfl_xor_sync(0xffffffffu, lrow[h2], 2);
+      }
+#pragma unroll
+      for (int kt = 0; kt < 2; ++kt) {
+        uint32_t ph[4], pl[4];
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const float* c = sc[2 * kt + half];
+          const float h0 = bf16_round(c[0]), h1 = bf16_round(c[1]), h2_ = bf16_round(c[2]), h3 = bf16_round(c[3]);
+          ph[2 * half] = pack_bf16(h0, h1);
+          ph[2 * half + 1] = pack_bf16(h2_, h3);
+          pl[2 * half] = pack_bf16(c[0] - h0, c[1] - h1);
+          pl[2 * half + 1] = pack_bf16(c[2] - h2_, c[3] - h3);
+        }
+        const unsigned char* vr = vs_ + (kt * 16 + tq * 2) * v_stride + quad * 2;
+#pragma unroll
+        for (int nt = 0; nt < DVT; ++nt) {
+          if (nt * 8 < dv) {
+            const unsigned char* vp = vr + nt * 16;
+            const uint32_t b0 = (uint32_t)*reinterpret_cast<const unsigned short*>(vp) |
+                                ((uint32_t)*reinterpret_cast<const unsigned short*>(vp + v_stride) << 16);
+            const uint32_t b1 = (uint32_t)*reinterpret_cast<const unsigned short*>(vp + 8 * v_stride) |
+                                ((uint32_t)*reinterpret_cast<const unsigned short*>(vp + 9 * v_stride) << 16);
+            mma_bf16_16816(o[nt], ph, b0, b1);
+            mma_bf16_16816(o[nt], pl, b0, b1);
+          }
+        }
+      }
+    }
+    // this warp's partial of (map, head) into shared memory: [dv] o, then max and sum
+#pragma unroll
+    for (int h2 = 0; h2 < 2; ++h2) {
+      if (!live[h2]) continue;
+      float* r = red + ((size_t)(map * G + quad + 8 * h2) * SD_WARPS + warp) * red_stride;
+#pragma unroll
+      for (int nt = 0; nt < DVT; ++nt) {
+        const int d = nt * 8 + tq * 2;
+        if (d < dv) {
+          r[d] = o[nt][2 * h2];
+          r[d + 1] = o[nt][2 * h2 + 1];
+        }
+      }
+      if (tq == 0) {
+        r[dv] = mrow[h2];
+        r[dv + 1] = lrow[h2];
+      }
+    }
+  }
+  __syncthreads();
+  // the four warps' partials of each (map, head) added in warp order
+  for (int i = threadIdx.x; i < hpv * dv; i += blockDim.x) {
+    const int mg = i / dv, d = i - mg * dv;              // mg = map * G + head of the kv head
+    const float* r = red + (size_t)mg * SD_WARPS * red_stride;
+    float mx = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < SD_WARPS; ++w) mx = fmaxf(mx, r[w * red_stride + dv]);
+    float l = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < SD_WARPS; ++w) {
+      const float mw = r[w * red_stride + dv];
+      const float f = mw == -INFINITY ? 0.f : exp2f(mw - mx);
+      l = fmaf(r[w * red_stride + dv + 1], f, l);
+      acc = fmaf(r[w * red_stride + d], f, acc);
+    }
+    const int head = kvh * hpv + (mg % G) * maps + mg / G;
+    if (num_chunks > 1) {
+      const size_t slot = ((size_t)m * nq + head) * num_chunks + blockIdx.z;
+      part_o[slot * dv + d] = acc;
+      if (d == 0) {
+        part_ml[slot * 2] = mx * 0.6931471805599453f;
+        part_ml[slot * 2 + 1] = l;
+      }
+    } else {
+      const float v = acc / l;
+      const size_t at = ((size_t)m * nq + head) * dv + d;
+      if (out_f32) static_cast<float*>(out)[at] = v;
+      else static_cast<bf16*>(out)[at] = __float2bfloat16_rn(v);
+    }
+  }
+}
+
 // Whether the tensor-core kernel takes these sizes.
 static bool sa_mma_ok(int dtype, int nq, int nkv, int maps, int dk, int dv) {
   if (dtype != SNK_BF16 || nkv <= 0 || maps <= 0 || maps > 4 || nq % (nkv * maps)) return false;
@@ -634,6 +853,14 @@ SNK_API int snk_split_attention_tile_rows(int nq, int nkv, int maps, int dk, int
     return per_map / G;
   }
   return hpv <= 32 ? 32 / hpv : 0;
+}
+
+// Keys per chunk for rows that stand alone: SD_CHUNK where the tensor-core kernel serves them, else 256.
+SNK_API int snk_split_attention_decode_chunk(int nq, int nkv, int maps, int dk, int dv, int dtype) {
+  // rows of keys and values up to 288 bytes together: five blocks of the tensor-core kernel fit an SM.  Wider
+  // rows (two blocks an SM) were measured slower there than on the CUDA cores (1,209 against 905 us for 64
+  // rows over windows of 2,048 at 512 bytes a key).
+  return sa_mma_ok(dtype, nq, nkv, maps, dk, dv) && (maps * dk + dv) * 2 <= 288 ? SD_CHUNK : 256;
 }
 
 // tiles: int32 [num_tiles, 2] = (first row, rows <= tile_rows), consecutive rows of one request; null:
@@ -656,8 +883,31 @@ SNK_API int snk_split_attention(const void* q, const void* kpool, const void* vp
   if (num_chunks > 1 && (tiles || scratch == nullptr || chunk <= 0 || chunk % SA_TILE)) return SNK_ERR_SIZE;
   float* part_o = static_cast<float*>(scratch);
   float* part_ml = part_o ? part_o + (size_t)num_tiles * nq * num_chunks * dv : nullptr;
-  // rows that stand alone (decoded tokens) stay on the CUDA-core kernel: 16-row tiles with one row in use
-  // were measured slower there (1,363 against 905 us for 64 rows over windows of 2,048)
+  if (!tiles && chunk == SD_CHUNK && sa_mma_ok(dtype, nq, nkv, maps, dk, dv) && (uintptr_t)kpool % 16 == 0 &&
+      (uintptr_t)vpool % 16 == 0 && (uintptr_t)q % 4 == 0) {
+    // rows that stand alone, their keys in chunks of SD_CHUNK: the heads of a kv head on the rows of the MMA
+    const size_t smem = (size_t)SD_CHUNK * ((size_t)maps * dk * 2 + 16 + (size_t)dv * 2 + 16) +
+                        (size_t)hpv * SD_WARPS * (dv + 2) * sizeof(float);
+    if (smem > 227 * 1024) return SNK_ERR_SIZE;
+    dim3 grid(num_tiles, nkv, num_chunks);
+#define SD_MMA(DKS_, DVT_)                                                                                   \
+  do {                                                                                                       \
+    if (smem > 48 * 1024)                                                                                    \
+      cudaFuncSetAttribute(split_decode_mma_kernel<DKS_, DVT_>,                                              \
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                          \
+    snk_launch(split_decode_mma_kernel<DKS_, DVT_>, dim3(grid), dim3(SD_WARPS * 32), smem, stream,           \
+               static_cast<const bf16*>(q), static_cast<const bf16*>(kpool), static_cast<const bf16*>(vpool), \
+               block_table, max_pages, page_size, positions, row_seg, out, out_f32, nq, nkv, maps, dk, dv,   \
+               window, scale, bias, bias_len, num_chunks, part_o, part_ml);                                  \
+  } while (0)
+    if (dk <= 64 && dv <= 64) SD_MMA(4, 8);
+    else if (dk <= 64) SD_MMA(4, 16);
+    else if (dv <= 64) SD_MMA(8, 8);
+    else SD_MMA(8, 16);
+#undef SD_MMA
+    SNK_LAUNCH_CHECK();
+    return 0;
+  }
   if (tiles && sa_mma_ok(dtype, nq, nkv, maps, dk, dv) && (uintptr_t)kpool % 16 == 0 &&
       (uintptr_t)vpool % 16 == 0 && (uintptr_t)q % 4 == 0) {
     const int G = hpv / maps;

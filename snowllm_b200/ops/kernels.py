@@ -89,6 +89,7 @@ _SIGNATURES = {
     "attention_split": {
         "snk_split_prepare": [P, LL, I, I, I, P, P, I, I, F, P, I, F, P, P, P, I, I, P, P, P, I, I, I, I, I, I, I, I, P],
         "snk_split_attention_tile_rows": [I, I, I, I, I, I, I],
+        "snk_split_attention_decode_chunk": [I, I, I, I, I, I],
         "snk_split_attention": [P, P, P, P, I, I, P, P, P, I, I, P, I, I, I, I, I, I, I, F, P, I, I, I, P, I, P],
     },
     "mlstm": {
@@ -1183,14 +1184,21 @@ def split_attention_tile_rows(nq: int, nkv: int, maps: int, dk: int, dv: int, dt
 SPLIT_ATTENTION_CHUNK = 256
 
 
+def split_attention_decode_chunk(nq: int, nkv: int, maps: int, dk: int, dv: int, dtype) -> int:
+    """Keys per chunk when rows stand alone (decoded tokens): 128 where the tensor-core kernel takes the
+    sizes (a block brings its whole chunk in at once, 32 keys per warp), else 256."""
+    return int(fn("snk_split_attention_decode_chunk")(int(nq), int(nkv), int(maps), int(dk), int(dv), code_of(dtype)))
+
+
 def split_attention(q, kpool, vpool, block_table, page_size, positions, row_seg, scale, *, maps=1, window=None,
-                    bias=None, tiles=None, tile_rows=1, out_dtype=None, out=None, num_chunks=1, scratch=None):
+                    bias=None, tiles=None, tile_rows=1, out_dtype=None, out=None, num_chunks=1, scratch=None,
+                    chunk=SPLIT_ATTENTION_CHUNK):
     """Causal attention of q [M, nq, dk] (nq = heads * maps) over keys [pages, nkv, page_size, maps*dk] and
     values [pages, nkv, page_size, dv]; query head (h, map) reads the key at offset map*dk of its kv head.
     ``window``: the last ``window`` keys only.  ``bias`` float [nq, L]: added to the scaled score by
     distance min(i - j, L - 1).  ``tiles`` int32 [n, 2] = (first row, rows <= tile_rows) of consecutive
     rows of one request, covering the step; None: every row alone.  ``num_chunks`` > 1 (rows alone only):
-    a row's keys are cut into chunks of SPLIT_ATTENTION_CHUNK at absolute positions, one block each, and
+    a row's keys are cut into chunks of ``chunk`` (``split_attention_decode_chunk``) at absolute positions, one block each, and
     merged in chunk order (``num_chunks``: the most chunks a row spans; needs ``scratch`` bytes as
     ``attention_scratch_bytes`` says).  Scores, weights and sums are float; returns [M, nq, dv] in
     ``out_dtype`` (float32 or the compute dtype)."""
@@ -1243,11 +1251,11 @@ def split_attention(q, kpool, vpool, block_table, page_size, positions, row_seg,
         _ptr(q), _ptr(kpool), _ptr(vpool), _ptr(block_table), block_table.shape[1], page_size, _ptr(positions),
         _ptr(row_seg), _ptr(tiles), n_tiles, int(tile_rows), _ptr(out), int(out_dtype == torch.float32 and dtype != torch.float32),
         nq, nkv, int(maps), dk, dv, int(window or 0), float(scale), _ptr(bias),
-        bias.shape[1] if bias is not None else 0, SPLIT_ATTENTION_CHUNK, num_chunks, _ptr(scratch),
+        bias.shape[1] if bias is not None else 0, int(chunk), num_chunks, _ptr(scratch),
         code_of(dtype), _stream()), "split_attention", work=work)
     if num_chunks > 1:
         check(fn("snk_attention_merge")(_ptr(scratch), _ptr(positions), _ptr(out), M, nq, dv, int(window or 0),
-                                        SPLIT_ATTENTION_CHUNK, num_chunks, code_of(out_dtype), c_void_p(0), _stream()),
+                                        int(chunk), num_chunks, code_of(out_dtype), c_void_p(0), _stream()),
               "attention_merge", work=lambda: (M * nq * (dv + 2) * 4 * num_chunks + _nbytes(out), 0))
     return out
 

@@ -156,6 +156,9 @@ class MapsAttention(Part):
         return rows
 
     def bind(self, tensors):
+        self._decode_chunk = kernels.split_attention_decode_chunk(self.nq, self.num_kv_heads, self.maps, self.head_dim,
+                                                                  self.v_head_dim, self.dtype) \
+            if tensors["q_proj"].is_cuda else kernels.SPLIT_ATTENTION_CHUNK
         self.w_in = pad_rows(torch.cat(self._projection_rows(tensors), 0), 16)
         self.wo = tensors["out_proj"]
         self.q_norm = tensors.get("q_norm")
@@ -179,18 +182,19 @@ class MapsAttention(Part):
         decode_only = max(ctx.host_seg_len) <= 1
         tile_rows = kernels.split_attention_tile_rows(self.nq, self.num_kv_heads, self.maps, self.head_dim,
                                                       self.v_head_dim, self.dtype, decode_only)
-        num_chunks, scratch = 1, None
+        num_chunks, scratch, chunk = 1, None, kernels.SPLIT_ATTENTION_CHUNK
         if decode_only:
-            # rows of decoded tokens: their keys in chunks of 256, one block each, merged in chunk order
-            num_chunks = plan.chunks(ctx, self.window, None, kernels.SPLIT_ATTENTION_CHUNK)
+            # rows of decoded tokens: their keys in chunks, one block each, merged in chunk order
+            chunk = self._decode_chunk
+            num_chunks = plan.chunks(ctx, self.window, None, chunk)
             if self.window:                # a captured step plans for its longest sequence; a window spans fewer
-                num_chunks = min(num_chunks, (self.window - 1) // kernels.SPLIT_ATTENTION_CHUNK + 2)
+                num_chunks = min(num_chunks, (self.window - 1) // chunk + 2)
             if num_chunks > 1:
                 scratch = ctx.scratch(kernels.attention_scratch_bytes(ctx.M, self.nq, self.v_head_dim, num_chunks))
         out = kernels.split_attention(q, kpool, vpool, cache.block_table, cache.page_size, ctx.positions,
                                       ctx.row_seg, self.scale, maps=self.maps, window=self.window, bias=self.bias,
                                       tiles=attention_tiles(ctx, tile_rows), tile_rows=tile_rows,
-                                      out_dtype=out_dtype, num_chunks=num_chunks, scratch=scratch)
+                                      out_dtype=out_dtype, num_chunks=num_chunks, scratch=scratch, chunk=chunk)
         ctx.tap("attention_o", out)
         return proj, out
 
