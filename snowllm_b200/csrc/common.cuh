@@ -47,6 +47,15 @@ struct SmallVec {
   }
 };
 
+// The activation on the gate of a gated product's store: act(g) * u.  Codes as the `swiglu` argument of the
+// product entry points carries them: 1 silu, 2 relu, 3 gelu (tanh form).  (0: no gated store.)
+enum { SNK_GLU_SILU = 1, SNK_GLU_RELU = 2, SNK_GLU_GELU_TANH = 3 };
+__device__ __forceinline__ float glu_act(float g, int act) {
+  if (act == SNK_GLU_RELU) return fmaxf(g, 0.f);
+  if (act == SNK_GLU_GELU_TANH) return 0.5f * g * (1.f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g)));
+  return g / (1.f + expf(-g));
+}
+
 // Four consecutive outputs in the compute dtype, by one store (16-byte aligned for float, 8 for bfloat16).
 template <typename T> __device__ __forceinline__ void store4(T* p, float a, float b, float c, float d);
 template <> __device__ __forceinline__ void store4<float>(float* p, float a, float b, float c, float d) {

@@ -58,7 +58,7 @@ template <int MT, typename OutT, bool SWIGLU>
 __global__ void __launch_bounds__(SK_WARPS * 32)
 gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT* __restrict__ C, int M,
                    int N, int K, const int* __restrict__ a_rows, int a_div,
-                   const int* __restrict__ offsets) {
+                   const int* __restrict__ offsets, int act) {
 #if SK_PREFETCH_LINES > 0
   if (offsets == nullptr) {
     // A plain product's W is a constant and this block's 16 rows of it are known from the block's number
@@ -174,7 +174,7 @@ gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT*
             const int m = m0 + tok, n = n0 + r;
             if (m < row_end && n + 8 < N) {
               const float gate = red[1][tok][r], up = red[1][tok][r + 8];
-              C[(size_t)m * (N / 2) + n0 / 2 + r] = from_f<OutT>(gate / (1.f + expf(-gate)) * up);
+              C[(size_t)m * (N / 2) + n0 / 2 + r] = from_f<OutT>(glu_act(gate, act) * up);
             }
           }
         } else {
@@ -199,7 +199,7 @@ gemm_skinny_kernel(const bf16* __restrict__ A, const bf16* __restrict__ W, OutT*
             gate += red[w][tok][r];
             up += red[w][tok][r + 8];
           }
-          C[(size_t)m * (N / 2) + n0 / 2 + r] = from_f<OutT>(gate / (1.f + expf(-gate)) * up);
+          C[(size_t)m * (N / 2) + n0 / 2 + r] = from_f<OutT>(glu_act(gate, act) * up);
         }
       }
     } else {
@@ -226,13 +226,13 @@ static int launch_skinny(const void* A, const void* W, void* C, int M, int N, in
   const bf16 *a = static_cast<const bf16*>(A), *w = static_cast<const bf16*>(W);
   if (swiglu)
     snk_launch_cluster(gemm_skinny_kernel<MT, bf16, true>, grid, block, 0, stream, split, a, w,
-                       static_cast<bf16*>(C), M, N, K, a_rows, a_div, offsets);
+                       static_cast<bf16*>(C), M, N, K, a_rows, a_div, offsets, swiglu);
   else if (out_f32)
     snk_launch_cluster(gemm_skinny_kernel<MT, float, false>, grid, block, 0, stream, split, a, w,
-                       static_cast<float*>(C), M, N, K, a_rows, a_div, offsets);
+                       static_cast<float*>(C), M, N, K, a_rows, a_div, offsets, 0);
   else
     snk_launch_cluster(gemm_skinny_kernel<MT, bf16, false>, grid, block, 0, stream, split, a, w,
-                       static_cast<bf16*>(C), M, N, K, a_rows, a_div, offsets);
+                       static_cast<bf16*>(C), M, N, K, a_rows, a_div, offsets, 0);
   SNK_LAUNCH_CHECK();
   return 0;
 }

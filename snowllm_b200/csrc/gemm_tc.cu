@@ -121,12 +121,13 @@ __device__ __forceinline__ TcTile tc_tile(int tile, int row_tiles, int M, int N,
 }
 
 // SWIGLU: W holds gate and up rows interleaved in blocks of 8 (rows 16j..16j+7: gate of features
-// 8j..8j+7, rows 16j+8..16j+15: their up rows); the store is silu(gate) * up into C[M, N/2].
+// 8j..8j+7, rows 16j+8..16j+15: their up rows); the store is act(gate) * up into C[M, N/2], act by the code
+// that the entry point's `swiglu` argument carries (1 silu, 2 relu, 3 gelu in its tanh form).
 template <int BN, typename OutT, bool SWIGLU>
 __global__ void __launch_bounds__(TC_THREADS)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                OutT* __restrict__ C, int M, int N, int K, const int* __restrict__ offsets, int groups,
-               int row_tiles_bound, int splits) {
+               int row_tiles_bound, int splits, int act) {
   constexpr int STAGE_BYTES = (TC_BM + BN) * TC_BK * 2;
   constexpr int STAGES = TC_SMEM_TILES / STAGE_BYTES < TC_MAX_STAGES ? TC_SMEM_TILES / STAGE_BYTES : TC_MAX_STAGES;
   extern __shared__ unsigned char smem_raw[];
@@ -250,7 +251,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
           if (lane == 0) mbar_arrive(&sh->acc_empty[buf]);
         }
         if (!*aborted)
-          tc_store_piece<OutT, SWIGLU>(r, stage_out, lane, Cp, t.row0 + lane_group * 32, t.row_end, t.n0 + c0, N);
+          tc_store_piece<OutT, SWIGLU>(r, stage_out, lane, Cp, t.row0 + lane_group * 32, t.row_end, t.n0 + c0, N, act);
       }
       ++local;
     }
@@ -267,7 +268,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant_
 
 template <int BN, typename OutT, bool SWIGLU>
 static int launch_tc(const CUtensorMap& map_a, const CUtensorMap& map_w, void* C, int M, int N, int K,
-                     const int* offsets, int groups, int row_tiles, int splits, cudaStream_t stream) {
+                     const int* offsets, int groups, int row_tiles, int splits, cudaStream_t stream,
+                     int act = SNK_GLU_SILU) {
   constexpr int STAGE_BYTES = (TC_BM + BN) * TC_BK * 2;
   constexpr int STAGES = TC_SMEM_TILES / STAGE_BYTES < TC_MAX_STAGES ? TC_SMEM_TILES / STAGE_BYTES : TC_MAX_STAGES;
   const size_t smem = 1024 + (size_t)STAGES * STAGE_BYTES + sizeof(TcShared);
@@ -281,7 +283,7 @@ static int launch_tc(const CUtensorMap& map_a, const CUtensorMap& map_w, void* C
   const long long tiles = (long long)row_tiles * ((N + BN - 1) / BN) * splits;
   const int blocks = (int)(tiles < sms ? tiles : sms);     // one block per SM (shared memory), persistent
   snk_launch(gemm_tc_kernel<BN, OutT, SWIGLU>, dim3(blocks), dim3(TC_THREADS), smem, stream, map_a, map_w, static_cast<OutT*>(C), M, N, K,
-                                                                 offsets, groups, row_tiles, splits);
+                                                                 offsets, groups, row_tiles, splits, act);
   SNK_LAUNCH_CHECK();
   return 0;
 }
@@ -292,7 +294,8 @@ static int launch_tc(const CUtensorMap& map_a, const CUtensorMap& map_w, void* C
 // side; each part leaves its float partial product in a plane of scratch, and a second kernel adds the
 // planes in part order and stores C (converted, or through SwiGLU).
 template <typename OutT, bool SWIGLU>
-__global__ void splitk_reduce_kernel(const float* __restrict__ parts, OutT* __restrict__ C, int M, int N, int splits) {
+__global__ void splitk_reduce_kernel(const float* __restrict__ parts, OutT* __restrict__ C, int M, int N, int splits,
+                                     int act) {
   pdl_begin();
   const size_t plane = (size_t)M * N;
   if constexpr (SWIGLU) {
@@ -310,8 +313,8 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ parts, OutT* __re
     uint32_t o[4];
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      const __nv_bfloat162 v = __floats2bfloat162_rn(g[2 * j] / (1.f + expf(-g[2 * j])) * u[2 * j],
-                                                     g[2 * j + 1] / (1.f + expf(-g[2 * j + 1])) * u[2 * j + 1]);
+      const __nv_bfloat162 v = __floats2bfloat162_rn(glu_act(g[2 * j], act) * u[2 * j],
+                                                     glu_act(g[2 * j + 1], act) * u[2 * j + 1]);
       o[j] = *reinterpret_cast<const uint32_t*>(&v);
     }
     *reinterpret_cast<uint4*>(C + b * 8) = make_uint4(o[0], o[1], o[2], o[3]);   // row m, features 8*(b % (N/16))..
@@ -384,13 +387,13 @@ SNK_API int snk_gemm_tc(const void* A, const void* W, void* C, int M, int N, int
     const float* parts = static_cast<const float*>(scratch);
     const size_t work = swiglu ? (size_t)M * N / 16 : (size_t)M * N / 4;
     const dim3 grid((unsigned)((work + 255) / 256)), block(256);
-    if (swiglu) snk_launch(splitk_reduce_kernel<bf16, true>, grid, block, 0, stream, parts, static_cast<bf16*>(C), M, N, splits);
-    else if (out_f32) snk_launch(splitk_reduce_kernel<float, false>, grid, block, 0, stream, parts, static_cast<float*>(C), M, N, splits);
-    else snk_launch(splitk_reduce_kernel<bf16, false>, grid, block, 0, stream, parts, static_cast<bf16*>(C), M, N, splits);
+    if (swiglu) snk_launch(splitk_reduce_kernel<bf16, true>, grid, block, 0, stream, parts, static_cast<bf16*>(C), M, N, splits, swiglu);
+    else if (out_f32) snk_launch(splitk_reduce_kernel<float, false>, grid, block, 0, stream, parts, static_cast<float*>(C), M, N, splits, 0);
+    else snk_launch(splitk_reduce_kernel<bf16, false>, grid, block, 0, stream, parts, static_cast<bf16*>(C), M, N, splits, 0);
     SNK_LAUNCH_CHECK();
     return 0;
   }
-#define TC_GO(BN_, T_, S_) launch_tc<BN_, T_, S_>(map_a, map_w, C, M, N, K, offsets, groups, row_tiles, 1, stream)
+#define TC_GO(BN_, T_, S_) launch_tc<BN_, T_, S_>(map_a, map_w, C, M, N, K, offsets, groups, row_tiles, 1, stream, swiglu)
   if (swiglu) return wide ? TC_GO(256, bf16, true) : TC_GO(128, bf16, true);
   if (wide) return out_f32 ? TC_GO(256, float, false) : TC_GO(256, bf16, false);
   return out_f32 ? TC_GO(128, float, false) : TC_GO(128, bf16, false);

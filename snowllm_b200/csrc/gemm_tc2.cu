@@ -93,7 +93,7 @@ __device__ __forceinline__ T2Tile t2_tile(int tile, int row_tiles, int M, int N)
 template <typename OutT, bool SWIGLU>
 __global__ void __launch_bounds__(T2_THREADS)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                OutT* __restrict__ C, int M, int N, int K, int row_tiles) {
+                OutT* __restrict__ C, int M, int N, int K, int row_tiles, int act) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   T2Shared* sh = reinterpret_cast<T2Shared*>(tiles + (size_t)T2_STAGES * T2_STAGE_BYTES);
@@ -209,7 +209,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
         }
         if (!*aborted)
           tc_store_piece<OutT, SWIGLU>(r, stage_out, lane, C, t.row0 + (int)rank * T2_BM + lane_group * 32, t.row_end,
-                                       t.n0 + c0, N);
+                                       t.n0 + c0, N, act);
       }
       ++local;
     }
@@ -226,7 +226,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
 template <typename OutT, bool SWIGLU>
 static int launch_tc2(const CUtensorMap& map_a, const CUtensorMap& map_w, void* C, int M, int N, int K,
-                      int row_tiles, cudaStream_t stream) {
+                      int row_tiles, cudaStream_t stream, int act) {
   const size_t smem = 1024 + (size_t)T2_STAGES * T2_STAGE_BYTES + sizeof(T2Shared);
   static int sms = 0;
   if (sms == 0) {
@@ -238,7 +238,7 @@ static int launch_tc2(const CUtensorMap& map_a, const CUtensorMap& map_w, void* 
   const long long tiles = (long long)row_tiles * ((N + T2_BN - 1) / T2_BN);
   const int pairs = (int)(tiles < sms / 2 ? tiles : sms / 2);
   snk_launch_cluster3(gemm_tc2_kernel<OutT, SWIGLU>, dim3(2 * pairs), dim3(T2_THREADS), smem, stream, dim3(2, 1, 1),
-                      map_a, map_w, static_cast<OutT*>(C), M, N, K, row_tiles);
+                      map_a, map_w, static_cast<OutT*>(C), M, N, K, row_tiles, act);
   SNK_LAUNCH_CHECK();
   return 0;
 }
@@ -310,7 +310,7 @@ __device__ __forceinline__ int t2g_box(int half_rows) {
 template <typename OutT, bool SWIGLU>
 __global__ void __launch_bounds__(T2_THREADS)
 gemm_tc2_grouped_kernel(const __grid_constant__ T2GMaps maps, const __grid_constant__ CUtensorMap map_w,
-                        OutT* __restrict__ C, int N, int K, const int* __restrict__ offsets, int groups) {
+                        OutT* __restrict__ C, int N, int K, const int* __restrict__ offsets, int groups, int act) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   T2Shared* sh = reinterpret_cast<T2Shared*>(tiles + (size_t)T2_STAGES * T2G_STAGE_BYTES);
@@ -444,7 +444,7 @@ gemm_tc2_grouped_kernel(const __grid_constant__ T2GMaps maps, const __grid_const
             q[4 * c] = v.x; q[4 * c + 1] = v.y; q[4 * c + 2] = v.z; q[4 * c + 3] = v.w;
           }
           __syncwarp();
-          tc_store_piece<OutT, true>(q, stage_out, lane, C, t.row0 + c0, t.row_end, col0, N);
+          tc_store_piece<OutT, true>(q, stage_out, lane, C, t.row0 + c0, t.row_end, col0, N, act);
         } else {
           // a warp's store writes 32 neighbouring columns of one row
           if (col0 + lane < N) {
@@ -469,7 +469,7 @@ gemm_tc2_grouped_kernel(const __grid_constant__ T2GMaps maps, const __grid_const
 
 template <typename OutT, bool SWIGLU>
 static int launch_tc2_grouped(const T2GMaps& maps, const CUtensorMap& map_w, void* C, int M, int N, int K,
-                              const int* offsets, int groups, cudaStream_t stream) {
+                              const int* offsets, int groups, cudaStream_t stream, int act) {
   const size_t smem = 1024 + (size_t)T2_STAGES * T2G_STAGE_BYTES + sizeof(T2Shared) + (T2G_MAX_GROUPS + 1) * sizeof(int);
   static int sms = 0;
   if (sms == 0) {
@@ -482,7 +482,7 @@ static int launch_tc2_grouped(const T2GMaps& maps, const CUtensorMap& map_w, voi
   const long long items = ((long long)M / (2 * T2_BM) + groups) * ((N + T2_BN - 1) / T2_BN);
   const int pairs = (int)(items < sms / 2 ? items : sms / 2);
   snk_launch_cluster3(gemm_tc2_grouped_kernel<OutT, SWIGLU>, dim3(2 * pairs), dim3(T2_THREADS), smem, stream,
-                      dim3(2, 1, 1), maps, map_w, static_cast<OutT*>(C), N, K, offsets, groups);
+                      dim3(2, 1, 1), maps, map_w, static_cast<OutT*>(C), N, K, offsets, groups, act);
   SNK_LAUNCH_CHECK();
   return 0;
 }
@@ -504,9 +504,9 @@ SNK_API int snk_gemm_tc2(const void* A, const void* W, void* C, int M, int N, in
     CUtensorMap gw;
     const int rc = tensor_map(W, (long long)groups * N, K, T2_BM, T2_BK, &gw);
     if (rc) return rc;
-    if (swiglu) return launch_tc2_grouped<bf16, true>(maps, gw, C, M, N, K, offsets, groups, stream);
-    if (out_f32) return launch_tc2_grouped<float, false>(maps, gw, C, M, N, K, offsets, groups, stream);
-    return launch_tc2_grouped<bf16, false>(maps, gw, C, M, N, K, offsets, groups, stream);
+    if (swiglu) return launch_tc2_grouped<bf16, true>(maps, gw, C, M, N, K, offsets, groups, stream, swiglu);
+    if (out_f32) return launch_tc2_grouped<float, false>(maps, gw, C, M, N, K, offsets, groups, stream, 0);
+    return launch_tc2_grouped<bf16, false>(maps, gw, C, M, N, K, offsets, groups, stream, 0);
   }
   const int row_tiles = (M + 2 * T2_BM - 1) / (2 * T2_BM);
   if (row_tiles <= 0) return SNK_ERR_SIZE;
@@ -515,9 +515,9 @@ SNK_API int snk_gemm_tc2(const void* A, const void* W, void* C, int M, int N, in
   if (rc) return rc;
   rc = tensor_map(W, N, K, T2_BN / 2, T2_BK, &map_w);
   if (rc) return rc;
-  if (swiglu) return launch_tc2<bf16, true>(map_a, map_w, C, M, N, K, row_tiles, stream);
-  if (out_f32) return launch_tc2<float, false>(map_a, map_w, C, M, N, K, row_tiles, stream);
-  return launch_tc2<bf16, false>(map_a, map_w, C, M, N, K, row_tiles, stream);
+  if (swiglu) return launch_tc2<bf16, true>(map_a, map_w, C, M, N, K, row_tiles, stream, swiglu);
+  if (out_f32) return launch_tc2<float, false>(map_a, map_w, C, M, N, K, row_tiles, stream, 0);
+  return launch_tc2<bf16, false>(map_a, map_w, C, M, N, K, row_tiles, stream, 0);
 }
 
 // Test hook: with on != 0 the producers of later launches issue no loads, so that the bounded waits run out

@@ -63,7 +63,8 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 
 template <typename OutT, bool SWIGLU>
 __device__ __forceinline__ void tc_store_piece(const uint32_t (&r)[32], float* stage, int lane, OutT* __restrict__ C,
-                                               int first_row, int row_end, int col0, int N) {
+                                               int first_row, int row_end, int col0, int N,
+                                               int act = SNK_GLU_SILU) {
   if constexpr (SWIGLU) {
     // columns: 8 gates, their 8 ups, 8 gates, their 8 ups -> 16 outputs of this lane's row, two 16-byte stores
     // (measured: faster from the registers than through the staging tile, 106 against 123 us on 2048 x 14336 x 2048)
@@ -78,7 +79,7 @@ __device__ __forceinline__ void tc_store_piece(const uint32_t (&r)[32], float* s
         for (int j = 0; j < 4; ++j) {
           const float g0 = __uint_as_float(r[blk * 16 + 2 * j]), g1 = __uint_as_float(r[blk * 16 + 2 * j + 1]);
           const float u0 = __uint_as_float(r[blk * 16 + 8 + 2 * j]), u1 = __uint_as_float(r[blk * 16 + 9 + 2 * j]);
-          const __nv_bfloat162 v = __floats2bfloat162_rn(g0 / (1.f + expf(-g0)) * u0, g1 / (1.f + expf(-g1)) * u1);
+          const __nv_bfloat162 v = __floats2bfloat162_rn(glu_act(g0, act) * u0, glu_act(g1, act) * u1);
           p[j] = *reinterpret_cast<const uint32_t*>(&v);
         }
         *reinterpret_cast<uint4*>(dst + blk * 8) = make_uint4(p[0], p[1], p[2], p[3]);

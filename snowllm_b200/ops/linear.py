@@ -77,14 +77,27 @@ def interleave_gate_up(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return both.reshape(*lead, 2 * I, K).contiguous()
 
 
-def linear_swiglu(x: torch.Tensor, w13: torch.Tensor, interleaved: bool) -> torch.Tensor:
-    """silu(x Wg^T) * (x Wu^T) -> [M, I] with Wg, Wu held in one matrix w13 [2I, K] (plain halves, or
-    interleaved by 8).  With the interleaved layout the bfloat16 products apply SwiGLU at their store."""
+# the gated store's activation, as the products' ``swiglu`` argument carries it
+GLU_CODES = {"silu": 1, "relu": 2, "gelu_tanh": 3}
+
+
+def linear_glu(x: torch.Tensor, w13: torch.Tensor, interleaved: bool, activation: str = "silu") -> torch.Tensor:
+    """act(x Wg^T) * (x Wu^T) -> [M, I] with Wg, Wu held in one matrix w13 [2I, K] (plain halves, or
+    interleaved by 8) and ``activation`` one of silu, relu, gelu_tanh.  With the interleaved layout the
+    bfloat16 products apply the gate at their store; otherwise one elementwise kernel follows the product."""
     if interleaved and kernels.gemm_skinny_ok(x, w13):
+        code = GLU_CODES[activation]
         if x.shape[0] <= SKINNY_MAX_ROWS:
-            return kernels.gemm_skinny(x, w13, swiglu=True)
-        return _tc(x, w13, swiglu=True)
-    return kernels.swiglu(linear(x, w13), interleaved=interleaved)
+            return kernels.gemm_skinny(x, w13, swiglu=code)
+        return _tc(x, w13, swiglu=code)
+    if activation == "silu":
+        return kernels.swiglu(linear(x, w13), interleaved=interleaved)
+    return kernels.gated_act(linear(x, w13), activation, interleaved)
+
+
+def linear_swiglu(x: torch.Tensor, w13: torch.Tensor, interleaved: bool) -> torch.Tensor:
+    """``linear_glu`` with silu."""
+    return linear_glu(x, w13, interleaved, "silu")
 
 
 def grouped_linear_swiglu(x, w13, offsets, rows_out, max_rows_per_group, a_rows, a_div, interleaved: bool):

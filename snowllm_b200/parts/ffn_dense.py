@@ -6,7 +6,7 @@ from __future__ import annotations
 import torch
 
 from ..errors import ConfigError
-from ..ops import interleave_gate_up, kernels, linear, linear_swiglu
+from ..ops import interleave_gate_up, kernels, linear, linear_glu, linear_swiglu
 from .base import Part
 from .registry import register_ffn
 from .spec import TensorSpec
@@ -39,9 +39,9 @@ class SwiGLU(Part):
 
 
 class GatedFFN(SwiGLU):
-    """down(act(gate x) * up x) with ``activation`` one of silu, relu, gelu_tanh.  silu is the class
-    above (the products apply it at their store); the others run the fused gate|up product and then one
-    elementwise kernel."""
+    """down(act(gate x) * up x) with ``activation`` one of silu, relu, gelu_tanh: the bfloat16 products apply
+    the gate at their store (gate and up rows interleaved by 8); float32, and widths that are no multiple
+    of 8, run the product and then one elementwise kernel."""
 
     def __init__(self, dtype, names, *, hidden_size: int, intermediate_size: int, activation: str = "silu"):
         super().__init__(dtype, names, hidden_size=hidden_size, intermediate_size=intermediate_size)
@@ -50,9 +50,7 @@ class GatedFFN(SwiGLU):
         self.activation = activation
 
     def forward(self, ctx, x):
-        if self.activation == "silu":
-            return super().forward(ctx, x)
-        act = kernels.gated_act(linear(x, self.w13), self.activation, self.interleaved)
+        act = linear_glu(x, self.w13, self.interleaved, self.activation)
         return linear(act, self.w2, out_dtype=torch.float32)
 
 

@@ -318,3 +318,21 @@ def test_greedy_generation_through_the_engine(tmp_path, mixed, dtype, eager):
             assert float(row.max() - row[tok]) <= slack, (dtype, i, tok, int(row.argmax()))
     if not eager:
         assert engine.runner.graph_replays > 0
+
+
+@pytest.mark.parametrize("rows", [5, 100, 4200])
+@pytest.mark.parametrize("act", ["relu", "gelu_tanh", "silu"])
+def test_products_apply_the_gate_at_their_store(rows, act):
+    """The few-rows product, the tcgen05 product and the product on pairs of SMs, each with every activation,
+    against the plain gate on float64 products of the same bfloat16 operands."""
+    from snowllm_b200.ops import interleave_gate_up, linear_glu
+    g = torch.Generator().manual_seed(rows)
+    K, inter = 64, 48
+    x = torch.randn(rows, K, generator=g).to(torch.bfloat16)
+    gate = (torch.randn(inter, K, generator=g) * 0.3).to(torch.bfloat16)
+    up = (torch.randn(inter, K, generator=g) * 0.3).to(torch.bfloat16)
+    got = linear_glu(x.cuda(), interleave_gate_up(gate, up).cuda(), True, act)
+    want = plain.ACTIVATIONS[act](x.double() @ gate.double().T) * (x.double() @ up.double().T)
+    assert got.shape == (rows, inter)
+    assert bool(((got.cpu().double() - want).abs() <= 0.008 * want.abs() + 1e-3).all())     # one bfloat16 rounding
+    assert cases.relative_error(got.cpu(), want) < 0.003
