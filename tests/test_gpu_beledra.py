@@ -45,7 +45,10 @@ ALONE = {
     "bias_attention_no_ff_one_kv_head": [cases.attention_layer(heads=3, kv_heads=1, dim=8, vdim=16, window=5,
                                                                bias_rows=4, bias_max=9, ff=None)],
     "bias_attention_unaligned_rows": [cases.attention_layer(heads=2, kv_heads=2, dim=12, vdim=20, window=40)],
+    "bias_attention_three_heads_per_kv_head": [cases.attention_layer(heads=6, kv_heads=2, dim=16, vdim=8, window=23)],
     "diff_attention": [cases.diff_layer()],
+    "diff_attention_three_heads_one_kv_head": [cases.diff_layer(heads=3, kv_heads=1, dim=32, vdim=16, rot_dims=12,
+                                                                window=45)],
     "diff_attention_plain_rotation_over_the_whole_head": [cases.diff_layer(rot_dims=16, scaling=False, dim=16, vdim=32,
                                                                            heads=4, kv_heads=2, diff=0.7)],
     "diff_attention_no_rotation": [cases.diff_layer(rot_dims=0, window=64, dim=8, vdim=16)],
