@@ -347,6 +347,25 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<const uint32_t*>(&v);
 }
 __device__ __forceinline__ float bf16_round(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+// Four 8 x 8 matrices of 16-bit elements from shared memory, lane L giving the address of row L % 8 of matrix
+// L / 8.  Plain: a lane gets elements 2 (L % 4), + 1 of row L / 4 of each matrix (the B fragment of keys held
+// row by row); .trans: rows 2 (L % 4), + 1 of column L / 4 (the B fragment of values held key by key).
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* row) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* row) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+// 2^x by the special-function unit (two units in the last place; 2^-inf = 0)
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 template <int DKS, int DVT>
 __global__ void split_attention_mma_kernel(
@@ -488,13 +507,15 @@ __global__ void split_attention_mma_kernel(
 #pragma unroll
     for (int nt = 0; nt < 4; ++nt) {
       sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
-      const unsigned char* kr = ks_ + (nt * 8 + quad) * k_stride + (map * dk + tq * 2) * 2;
+      // lane L: row L % 8 of the tile's 8 keys, 8 elements from (L / 8) * 8 on: two k-steps per instruction
+      const unsigned char* kr = ks_ + (nt * 8 + (lane & 7)) * k_stride + (map * dk + (lane >> 3) * 8) * 2;
 #pragma unroll
-      for (int ks = 0; ks < DKS; ++ks) {
-        if (ks * 16 < dk) {
-          const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kr + ks * 32);
-          const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kr + ks * 32 + 16);
-          mma_bf16_16816(sc[nt], qa[ks], b0, b1);
+      for (int kp = 0; kp < DKS / 2; ++kp) {
+        if (kp * 32 < dk) {
+          uint32_t b[4];
+          ldsm_x4(b, kr + kp * 64);
+          mma_bf16_16816(sc[nt], qa[2 * kp], b[0], b[1]);
+          if (kp * 32 + 16 < dk) mma_bf16_16816(sc[nt], qa[2 * kp + 1], b[2], b[3]);
         }
       }
     }
@@ -524,7 +545,7 @@ __global__ void split_attention_mma_kernel(
       tmax[h2] = fmaxf(tmax[h2], __shfl_xor_sync(0xffffffffu, tmax[h2], 2));
       const float m_new = fmaxf(mx[h2], tmax[h2]);
       // a row without a key so far keeps -inf: its weights are 0 and its correction 1
-      corr[h2] = m_new == -INFINITY ? 1.f : exp2f(mx[h2] - m_new);
+      corr[h2] = m_new == -INFINITY ? 1.f : ex2_approx(mx[h2] - m_new);
       mx[h2] = m_new;
     }
     float psum[2] = {0.f, 0.f};
@@ -533,7 +554,7 @@ __global__ void split_attention_mma_kernel(
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
         const int h2 = e >> 1;
-        const float pw = sc[nt][e] == -INFINITY ? 0.f : exp2f(sc[nt][e] - mx[h2]);
+        const float pw = mx[h2] == -INFINITY ? 0.f : ex2_approx(sc[nt][e] - mx[h2]);
         sc[nt][e] = pw;
         psum[h2] += pw;
       }
@@ -562,17 +583,20 @@ __global__ void split_attention_mma_kernel(
         pl[2 * half] = pack_bf16(c[0] - h0, c[1] - h1);
         pl[2 * half + 1] = pack_bf16(c[2] - h2_, c[3] - h3);
       }
-      const unsigned char* vr = vs_ + (kt * 16 + tq * 2) * v_stride + quad * 2;
+      // lane L: key (L / 8 % 2) * 8 + L % 8 of the step's 16, 8 columns from (L / 16) * 8 on: two column tiles
+      // per instruction (a last, odd tile reads the row's pad and is not used)
+      const unsigned char* vr = vs_ + (kt * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * v_stride + (lane >> 4) * 16;
 #pragma unroll
-      for (int nt = 0; nt < DVT; ++nt) {
-        if (nt * 8 < dv) {
-          const unsigned char* vp = vr + nt * 16;
-          const uint32_t b0 = (uint32_t)*reinterpret_cast<const unsigned short*>(vp) |
-                              ((uint32_t)*reinterpret_cast<const unsigned short*>(vp + v_stride) << 16);
-          const uint32_t b1 = (uint32_t)*reinterpret_cast<const unsigned short*>(vp + 8 * v_stride) |
-                              ((uint32_t)*reinterpret_cast<const unsigned short*>(vp + 9 * v_stride) << 16);
-          mma_bf16_16816(o[nt], ph, b0, b1);
-          mma_bf16_16816(o[nt], pl, b0, b1);
+      for (int np = 0; np < DVT / 2; ++np) {
+        if (np * 16 < dv) {
+          uint32_t b[4];
+          ldsm_x4_trans(b, vr + np * 32);
+          mma_bf16_16816(o[2 * np], ph, b[0], b[1]);
+          mma_bf16_16816(o[2 * np], pl, b[0], b[1]);
+          if (np * 16 + 8 < dv) {
+            mma_bf16_16816(o[2 * np + 1], ph, b[2], b[3]);
+            mma_bf16_16816(o[2 * np + 1], pl, b[2], b[3]);
+          }
         }
       }
     }
@@ -711,13 +735,15 @@ split_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kpo
 #pragma unroll
       for (int nt = 0; nt < 4; ++nt) {
         sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
-        const unsigned char* kr = ks_ + (nt * 8 + quad) * k_stride + (map * dk + tq * 2) * 2;
+        // lane L: row L % 8 of the tile's 8 keys, 8 elements from (L / 8) * 8 on: two k-steps per instruction
+        const unsigned char* kr = ks_ + (nt * 8 + (lane & 7)) * k_stride + (map * dk + (lane >> 3) * 8) * 2;
 #pragma unroll
-        for (int ks = 0; ks < DKS; ++ks) {
-          if (ks * 16 < dk) {
-            const uint32_t b0 = *reinterpret_cast<const uint32_t*>(kr + ks * 32);
-            const uint32_t b1 = *reinterpret_cast<const uint32_t*>(kr + ks * 32 + 16);
-            mma_bf16_16816(sc[nt], qa[ks], b0, b1);
+        for (int kp = 0; kp < DKS / 2; ++kp) {
+          if (kp * 32 < dk) {
+            uint32_t b[4];
+            ldsm_x4(b, kr + kp * 64);
+            mma_bf16_16816(sc[nt], qa[2 * kp], b[0], b[1]);
+            if (kp * 32 + 16 < dk) mma_bf16_16816(sc[nt], qa[2 * kp + 1], b[2], b[3]);
           }
         }
       }
@@ -746,7 +772,7 @@ split_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kpo
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const int h2 = e >> 1;
-          const float pw = sc[nt][e] == -INFINITY ? 0.f : exp2f(sc[nt][e] - mrow[h2]);
+          const float pw = mrow[h2] == -INFINITY ? 0.f : ex2_approx(sc[nt][e] - mrow[h2]);
           sc[nt][e] = pw;
           lrow[h2] += pw;
         }
@@ -768,17 +794,20 @@ split_decode_mma_kernel(const bf16* __restrict__ q, const bf16* __restrict__ kpo
           pl[2 * half] = pack_bf16(c[0] - h0, c[1] - h1);
           pl[2 * half + 1] = pack_bf16(c[2] - h2_, c[3] - h3);
         }
-        const unsigned char* vr = vs_ + (kt * 16 + tq * 2) * v_stride + quad * 2;
+        // lane L: key (L / 8 % 2) * 8 + L % 8 of the step's 16, 8 columns from (L / 16) * 8 on: two column tiles
+        // per instruction (a last, odd tile reads the row's pad and is not used)
+        const unsigned char* vr = vs_ + (kt * 16 + ((lane >> 3) & 1) * 8 + (lane & 7)) * v_stride + (lane >> 4) * 16;
 #pragma unroll
-        for (int nt = 0; nt < DVT; ++nt) {
-          if (nt * 8 < dv) {
-            const unsigned char* vp = vr + nt * 16;
-            const uint32_t b0 = (uint32_t)*reinterpret_cast<const unsigned short*>(vp) |
-                                ((uint32_t)*reinterpret_cast<const unsigned short*>(vp + v_stride) << 16);
-            const uint32_t b1 = (uint32_t)*reinterpret_cast<const unsigned short*>(vp + 8 * v_stride) |
-                                ((uint32_t)*reinterpret_cast<const unsigned short*>(vp + 9 * v_stride) << 16);
-            mma_bf16_16816(o[nt], ph, b0, b1);
-            mma_bf16_16816(o[nt], pl, b0, b1);
+        for (int np = 0; np < DVT / 2; ++np) {
+          if (np * 16 < dv) {
+            uint32_t b[4];
+            ldsm_x4_trans(b, vr + np * 32);
+            mma_bf16_16816(o[2 * np], ph, b[0], b[1]);
+            mma_bf16_16816(o[2 * np], pl, b[0], b[1]);
+            if (np * 16 + 8 < dv) {
+              mma_bf16_16816(o[2 * np + 1], ph, b[2], b[3]);
+              mma_bf16_16816(o[2 * np + 1], pl, b[2], b[3]);
+            }
           }
         }
       }
