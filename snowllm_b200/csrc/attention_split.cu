@@ -886,10 +886,15 @@ SNK_API int snk_split_attention_tile_rows(int nq, int nkv, int maps, int dk, int
 
 // Keys per chunk for rows that stand alone: SD_CHUNK where the tensor-core kernel serves them, else 256.
 SNK_API int snk_split_attention_decode_chunk(int nq, int nkv, int maps, int dk, int dv, int dtype) {
-  // rows of keys and values up to 288 bytes together: five blocks of the tensor-core kernel fit an SM.  Wider
-  // rows (two blocks an SM) were measured slower there than on the CUDA cores (1,209 against 905 us for 64
-  // rows over windows of 2,048 at 512 bytes a key).
-  return sa_mma_ok(dtype, nq, nkv, maps, dk, dv) && (maps * dk + dv) * 2 <= 288 ? SD_CHUNK : 256;
+  // Rows of keys and values up to 1,024 bytes together go to the tensor-core kernel.  Measured at 512 bytes a key
+  // (two blocks an SM) against the CUDA-core kernel: the same at 64 rows (907 us for four launches over windows of
+  // 2,048), faster at 8 rows (a step 0.916 against 0.998 ms); at 256 bytes a key 448 against 634 us.
+  static int widest = -1;                                  // SNOWLLM_B200_DECODE_MMA_ROW_BYTES: another bound, for A/B runs
+  if (widest < 0) {
+    const char* e = getenv("SNOWLLM_B200_DECODE_MMA_ROW_BYTES");
+    widest = e ? atoi(e) : 1024;
+  }
+  return sa_mma_ok(dtype, nq, nkv, maps, dk, dv) && (maps * dk + dv) * 2 <= widest ? SD_CHUNK : 256;
 }
 
 // tiles: int32 [num_tiles, 2] = (first row, rows <= tile_rows), consecutive rows of one request; null:
