@@ -523,19 +523,38 @@ __global__ void split_attention_mma_kernel(
     // (scores and maxima are kept in units of log 2: the weights are 2^(s - m), one instruction each)
     float tmax[2] = {-INFINITY, -INFINITY};
     const bool inner = t0 >= max(klo[0], klo[1]) && t0 + SA_TILE - 1 <= min(khi[0], khi[1]);   // no key is masked
+    if (inner) {
+      const float* brow[2] = {bias ? bias + (size_t)head[0] * bias_len : nullptr,
+                              bias ? bias + (size_t)head[1] * bias_len : nullptr};
 #pragma unroll
-    for (int nt = 0; nt < 4; ++nt) {
+      for (int nt = 0; nt < 4; ++nt) {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int h2 = e >> 1;
-        const int kp = t0 + nt * 8 + tq * 2 + (e & 1);
-        float s = sc[nt][e] * scale2;
-        const bool valid = inner || (kp >= klo[h2] && kp <= khi[h2]);
-        if (bias && valid)
-          s = fmaf(bias[(size_t)head[h2] * bias_len + min(p_row[h2] - kp, bias_len - 1)], 1.4426950408889634f, s);
-        s = valid ? s : -INFINITY;
-        sc[nt][e] = s;
-        tmax[h2] = fmaxf(tmax[h2], s);
+        for (int e = 0; e < 4; ++e) {
+          const int h2 = e >> 1;
+          float s = sc[nt][e] * scale2;
+          if (bias) {
+            const int dist = p_row[h2] - (t0 + nt * 8 + tq * 2 + (e & 1));
+            s = fmaf(brow[h2][min(dist, bias_len - 1)], 1.4426950408889634f, s);
+          }
+          sc[nt][e] = s;
+          tmax[h2] = fmaxf(tmax[h2], s);
+        }
+      }
+    } else {
+#pragma unroll
+      for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int h2 = e >> 1;
+          const int kp = t0 + nt * 8 + tq * 2 + (e & 1);
+          float s = sc[nt][e] * scale2;
+          const bool valid = kp >= klo[h2] && kp <= khi[h2];
+          if (bias && valid)
+            s = fmaf(bias[(size_t)head[h2] * bias_len + min(p_row[h2] - kp, bias_len - 1)], 1.4426950408889634f, s);
+          s = valid ? s : -INFINITY;
+          sc[nt][e] = s;
+          tmax[h2] = fmaxf(tmax[h2], s);
+        }
       }
     }
     float corr[2];

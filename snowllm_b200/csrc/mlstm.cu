@@ -116,6 +116,9 @@ mlstm_kernel(const float* __restrict__ proj, long long ld, int q_off, int k_off,
     }
     __syncthreads();
     m = g_m[nt - 1];
+    // Only S and n pass from one token to the next (one multiply-add each); the sums, shuffles and the division of
+    // neighbouring tokens are independent, so four tokens' worth of them are kept in flight.
+#pragma unroll 4
     for (int t = 0; t < nt; ++t) {
       const float keep = g_keep[t], take = g_take[t];
       const float* qt = qs + t * dkp;
