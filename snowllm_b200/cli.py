@@ -46,7 +46,7 @@ def parser() -> argparse.ArgumentParser:
     p = argparse.ArgumentParser(
         prog="snowllm_b200",
         usage="snowllm_b200 PATH [options]\n       snowllm_b200 random-weights CONFIG OUT [options]",
-        description="Generate with an LFM2.5 model folder (config.json + safetensors) on one B200.")
+        description="Generate with a model folder (config.json + safetensors; LFM2.5 or Beledra) on one B200.")
     g = p.add_argument_group("generation")
     g.add_argument("model", metavar="PATH", help="Checkpoint directory.")
     g.add_argument("--prompt-ids", action="append", type=_ids, default=[], metavar="IDS",

@@ -193,3 +193,24 @@ def test_bench_design_option_builds_both_models_at_equal_size():
         kinds = [type(b.mixer).__name__ for b in ours.blocks]
         assert {"BiasAttention", "DiffAttention", "MLstm"} == set(kinds)
         assert any(e.cache_of is not None for e in ours.run)
+
+
+def test_command_line_writes_a_model_folder_that_the_loader_accepts(tmp_path):
+    """``random-weights`` through the command line's own entry point, then the folder against the model's
+    declarations (names, shapes, the bias table's rows from the optional key)."""
+    from snowllm_b200 import cli
+    from snowllm_b200.weights.loader import check_against
+    from snowllm_b200.weights.safetensors_io import Checkpoint
+    src = tmp_path / "config.json"
+    src.write_text(json.dumps(cases.MIXED))
+    out = tmp_path / "model"
+    assert cli.main(["random-weights", str(src), str(out), "--seed", "3"]) == 0
+    arch, cfg, _ = read_config_json(out)
+    assert arch.name == "Beledra" and cfg == read_beledra_config(cases.MIXED)
+    model = build_model(out, "bfloat16")
+    ck = Checkpoint(out)
+    try:
+        check_against([s for _, s in model.declare(ck.has)], ck.names(), ck.meta)
+        assert tuple(ck.meta("l0.mix.rel")[1]) == (12, 4) and tuple(ck.meta("l2.mix.i.b")[1]) == (2,)
+    finally:
+        ck.close()

@@ -339,3 +339,21 @@ def test_products_apply_the_gate_at_their_store(rows, act):
     assert got.shape == (rows, inter)
     assert bool(((got.cpu().double() - want).abs() <= 0.008 * want.abs() + 1e-3).all())     # one bfloat16 rounding
     assert cases.relative_error(got.cpu(), want) < 0.003
+
+
+def test_command_line_generates_with_the_design(tmp_path, mixed, capsys):
+    import json
+
+    from snowllm_b200 import cli
+    tensors, prompts, _ = mixed
+    cases.write_folder(tmp_path, cases.MIXED, tensors)
+    prompt = prompts["b"][:20]
+    rc = cli.main([str(tmp_path), "--prompt-ids", ",".join(map(str, prompt)), "--default-max-tokens", "12",
+                   "--dtype", "float32", "--max-model-len", "256", "--kv-block-size", "16", "--max-num-seqs", "2"])
+    assert rc == 0
+    line = json.loads(capsys.readouterr().out.strip().splitlines()[0])
+    assert line["prompt_tokens"] == 20 and len(line["tokens"]) == 12 and line["finish_reason"] == "length"
+    logits = reference(cases.MIXED, tensors, prompt + line["tokens"])
+    for i, tok in enumerate(line["tokens"]):
+        row = logits[len(prompt) - 1 + i]
+        assert float(row.max() - row[tok]) <= 1e-4
