@@ -88,7 +88,7 @@ def _beledra(width: int, layers: int, ff: int, vocab: int = 65536) -> dict:
                       "mask": {"size": 1024}, "bias_max": 768, "bias_rows": 32}}
     diff = {"type": "attention_2", "mlp": {"kind": "dense", "ff": ff},
             "mixer": {"heads": heads // 2, "kv_heads": heads // 8, "dim": 64, "vdim": 128, "scale": 0.125,
-                      "mask": {"size": 2048}, "diff": 0.5,
+                      "mask": {"size": 2048}, "diff": 0.4,
                       "rot": {"dims": 64, "base": 1000000.0,
                               "scaling": {"factor": 4.0, "original": 8192, "fast": 32.0, "slow": 1.0}}}}
     memory = {"type": "mlstm", "mlp": None,

@@ -202,7 +202,7 @@ class MapsAttention(Part):
 class BiasAttention(MapsAttention):
     """One map per head and a learned bias per (distance bucket, head)."""
 
-    DEFAULT_ROWS = 32          # rows of a drawn table when the configuration names none
+    DEFAULT_ROWS = 16          # rows of a drawn table when the configuration names none
 
     def __init__(self, dtype, names, *, bias_far: float, bias_rows: int | None = None, **kw):
         super().__init__(dtype, names, **kw)

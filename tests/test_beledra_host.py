@@ -95,7 +95,7 @@ def test_bias_table_rows_come_from_the_checkpoint():
     assert "l3.mix.lq1" in str(e.value) and "l3.mix.k" in str(e.value)
 
 
-@pytest.mark.parametrize("rows,far", [(12, 40), (32, 120), (6, 17), (8, 64), (16, 128), (2, 5), (9, 30.5)])
+@pytest.mark.parametrize("rows,far", [(12, 40), (24, 200), (6, 17), (8, 64), (16, 128), (2, 5), (9, 30.5)])
 def test_distance_buckets_follow_the_formula(rows, far):
     b = DistanceBuckets(rows, far)
     for n in range(0, 400):
@@ -123,7 +123,7 @@ def test_an_exact_step_takes_the_upper_bucket():
 
 @pytest.mark.parametrize("rot", [
     {"dims": 8, "base": 500.0, "scaling": {"factor": 4.0, "original": 64, "fast": 8.0, "slow": 1.0}},
-    {"dims": 24, "base": 20000.0, "scaling": {"factor": 2.0, "original": 4096, "fast": 32.0, "slow": 1.0}},
+    {"dims": 20, "base": 50000.0, "scaling": {"factor": 3.0, "original": 4096, "fast": 16.0, "slow": 2.0}},
     {"dims": 16, "base": 10000.0, "scaling": {"factor": 8.0, "original": 512, "fast": 4.0, "slow": 0.5}},
     {"dims": 6, "base": 100.0},
 ])
