@@ -584,3 +584,31 @@ SNK_API int snk_moe_combine(const float* y, const int* pair_pos, const float* to
   SNK_LAUNCH_CHECK();
   return 0;
 }
+
+// ---------------------------------------------------------------------------------------
+// Experts whose weight multiplies their INPUT: out[r, :] = x[pair / k, :] * w[pair] with pair = sorted_pair[r]
+// (the (token, pick) pairs in expert order), in the compute dtype; ones[pair] = 1, the weights the sum of the
+// experts' outputs is then formed with.  One block per sorted row.
+template <typename T>
+__global__ void moe_scaled_rows_kernel(const T* __restrict__ x, const int* __restrict__ sorted_pair,
+                                       const float* __restrict__ w, T* __restrict__ out, float* __restrict__ ones,
+                                       int K, int k) {
+  pdl_begin();
+  const size_t r = blockIdx.x;
+  const int pair = sorted_pair[r];
+  const float s = w[pair];
+  const T* src = x + (size_t)(pair / k) * K;
+  for (int i = threadIdx.x; i < K; i += blockDim.x) out[r * K + i] = from_f<T>(to_f<T>(src[i]) * s);
+  if (threadIdx.x == 0) ones[pair] = 1.f;
+}
+
+SNK_API int snk_moe_scaled_rows(const void* x, const int* sorted_pair, const float* w, void* out, float* ones,
+                                int R, int K, int k, int dtype, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (K <= 0 || k <= 0) return SNK_ERR_SIZE;
+  const int threads = K >= 1024 ? 256 : 128;
+  SNK_DISPATCH(dtype, snk_launch(moe_scaled_rows_kernel<T>, dim3(R), dim3(threads), 0, stream,
+                                 static_cast<const T*>(x), sorted_pair, w, static_cast<T*>(out), ones, K, k));
+  SNK_LAUNCH_CHECK();
+  return 0;
+}

@@ -4,6 +4,11 @@
 //                    sum again in the compute dtype: what the next sublayer reads
 //   cast_rows:       the float residual in the compute dtype (the first sublayer's input)
 //   gated_act:       out = act(gate) * up over [M, 2I] -> [M, I], act one of silu, relu, gelu (tanh form)
+//   act_rows:        out = act(x), act one of silu, relu, gelu (tanh form), relu squared
+//   rms_cols:        columns [off, off + n) of each row divided by their root mean square, times a weight
+//   add_dyt:         residual += (a + b) for up to two float deltas (the second may be routed experts' outputs
+//                    still in pieces), then the Dynamic Tanh norm tanh(alpha * x) * w + b of the sum: a norm
+//                    without mean or variance
 //   head_norm_gate:  per (row, head): o = a (- lambda * b), o / sqrt(mean(o^2) + eps) (* w) * mult
 //                    * sigmoid(g): the end of a mixer whose heads are normalised one by one and gated
 //
@@ -11,10 +16,14 @@
 // at the store.
 #include "common.cuh"
 
-enum { ACT_SILU = 0, ACT_RELU = 1, ACT_GELU_TANH = 2 };
+enum { ACT_SILU = 0, ACT_RELU = 1, ACT_GELU_TANH = 2, ACT_RELU2 = 3 };
 
 __device__ __forceinline__ float act_apply(float z, int act) {
   if (act == ACT_RELU) return fmaxf(z, 0.f);
+  if (act == ACT_RELU2) {
+    const float p = fmaxf(z, 0.f);
+    return p * p;
+  }
   if (act == ACT_GELU_TANH)
     return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
   return z / (1.f + expf(-z));
@@ -110,7 +119,7 @@ __global__ void gated_act_kernel(const T* __restrict__ gate_up, T* __restrict__ 
 SNK_API int snk_gated_act(const void* gate_up, void* out, int M, int inter, int interleaved, int act, int dtype,
                           cudaStream_t stream) {
   if (M <= 0 || inter <= 0) return 0;
-  if (act < 0 || act > ACT_GELU_TANH || (interleaved && inter % 8)) return SNK_ERR_SIZE;
+  if (act < 0 || act > ACT_RELU2 || (interleaved && inter % 8)) return SNK_ERR_SIZE;
   const long long n = (long long)M * inter;
   const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
   SNK_DISPATCH(dtype, snk_launch(gated_act_kernel<T>, dim3(blocks), dim3(256), 0, stream,
@@ -166,6 +175,99 @@ SNK_API int snk_head_norm_gate(const float* a, int a_stride, int second, float l
   SNK_DISPATCH(dtype, snk_launch(head_norm_gate_kernel<T>, dim3((unsigned)blocks), dim3(warps * 32), 0, stream,
                                  a, a_stride, second, lambda, SmallVec{w, w_f32}, (int)(w != nullptr),
                                  SmallVec{g, g_f32}, (int)(g != nullptr), g_ld, static_cast<T*>(out), M, heads, dv, eps, mult));
+  SNK_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void act_rows_kernel(const T* __restrict__ x, T* __restrict__ out, long long n, int act) {
+  pdl_begin();
+  const long long stride = (long long)gridDim.x * blockDim.x;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
+    out[i] = from_f<T>(act_apply(to_f<T>(x[i]), act));
+}
+
+SNK_API int snk_act_rows(const void* x, void* out, long long n, int act, int dtype, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (act < 0 || act > ACT_RELU2) return SNK_ERR_SIZE;
+  const int blocks = (int)((n + 255) / 256 < 148 * 16 ? (n + 255) / 256 : 148 * 16);
+  SNK_DISPATCH(dtype, snk_launch(act_rows_kernel<T>, dim3(blocks), dim3(256), 0, stream, static_cast<const T*>(x),
+                                 static_cast<T*>(out), n, act));
+  SNK_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// One warp per row: out[m, 0:n) = x[m, off + (0:n)] / sqrt(mean(x^2) + eps) * w.
+template <typename T>
+__global__ void rms_cols_kernel(const T* __restrict__ x, long long ld, int off, SmallVec w, T* __restrict__ out,
+                                int M, int n, float eps) {
+  pdl_begin();
+  const int lane = threadIdx.x & 31;
+  const long long m = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (m >= M) return;
+  const T* row = x + m * ld + off;
+  float ss = 0.f;
+  for (int c = lane; c < n; c += 32) {
+    const float v = to_f<T>(row[c]);
+    ss = fmaf(v, v, ss);
+  }
+  ss = warp_sum(ss);
+  const float inv = 1.f / sqrtf(ss / (float)n + eps);
+  for (int c = lane; c < n; c += 32) out[m * n + c] = from_f<T>(to_f<T>(row[c]) * inv * w[c]);
+}
+
+SNK_API int snk_rms_cols(const void* x, long long ld, int off, const void* w, int w_f32, void* out, int M, int n,
+                         float eps, int dtype, cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (n <= 0 || off < 0 || ld < off + n) return SNK_ERR_SIZE;
+  const int warps = 4;
+  SNK_DISPATCH(dtype, snk_launch(rms_cols_kernel<T>, dim3((M + warps - 1) / warps), dim3(warps * 32), 0, stream,
+                                 static_cast<const T*>(x), ld, off, SmallVec{w, w_f32}, static_cast<T*>(out), M, n,
+                                 eps));
+  SNK_LAUNCH_CHECK();
+  return 0;
+}
+
+// ---------------------------------------------------------------------------------------------
+// One block per output row.  rows (may be null): the rows to normalise, the residual then stays as it is.
+// da, db (may be null): float deltas [M, H].  y, pair_pos, pw, k (k = 0: none): routed experts' outputs
+// [pairs, H], where each (row, pick) pair's row lies, and the picks' weights.
+template <typename T>
+__global__ void add_dyt_kernel(float* __restrict__ residual, const float* __restrict__ da,
+                               const float* __restrict__ db, const float* __restrict__ y,
+                               const int* __restrict__ pair_pos, const float* __restrict__ pw, int k, SmallVec w,
+                               SmallVec b, SmallVec alpha, T* __restrict__ out, const int* __restrict__ rows, int H) {
+  pdl_begin();
+  const size_t m = rows ? rows[blockIdx.x] : blockIdx.x;
+  const float al = alpha[0];
+  for (int i = threadIdx.x; i < H; i += blockDim.x) {
+    float v = residual[m * H + i];
+    if (da || db || k) {
+      float d = da ? da[m * H + i] : 0.f;
+      if (db) d += db[m * H + i];
+      if (k) {
+        float e = 0.f;
+        for (int j = 0; j < k; ++j) e = fmaf(pw[m * k + j], y[(size_t)pair_pos[m * k + j] * H + i], e);
+        d += e;
+      }
+      v += d;
+      if (!rows) residual[m * H + i] = v;
+    }
+    out[(size_t)blockIdx.x * H + i] = from_f<T>(tanhf(al * v) * w[i] + b[i]);
+  }
+}
+
+SNK_API int snk_add_dyt(float* residual, const float* da, const float* db, const float* y, const int* pair_pos,
+                        const float* pw, int k, const void* w, const void* b, const void* alpha, int small_f32,
+                        void* out, const int* rows, int R, int H, int dtype, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (H <= 0 || k < 0) return SNK_ERR_SIZE;
+  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+  SNK_DISPATCH(dtype, snk_launch(add_dyt_kernel<T>, dim3(R), dim3(threads), 0, stream, residual, da, db, y, pair_pos,
+                                 pw, k, SmallVec{w, small_f32}, SmallVec{b, small_f32}, SmallVec{alpha, small_f32},
+                                 static_cast<T*>(out), rows, H));
   SNK_LAUNCH_CHECK();
   return 0;
 }

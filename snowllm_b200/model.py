@@ -27,7 +27,10 @@ class Model:
         self.blocks = []
         for layer in spec.layers:
             block_cls = lookup("block", layer.block)
-            if (layer.ffn is None) != (layer.ffn_norm is None):
+            if getattr(block_cls, "single_norm", False):
+                if layer.ffn_norm is not None:
+                    raise ConfigError(f"a {layer.block!r} layer has one norm for both sublayers")
+            elif (layer.ffn is None) != (layer.ffn_norm is None):
                 raise ConfigError("a layer has a feed-forward and its norm, or neither")
             self.blocks.append(block_cls(_make("mixer", layer.mixer, dtype),
                                          _make("ffn", layer.ffn, dtype) if layer.ffn is not None else None,

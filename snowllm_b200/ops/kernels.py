@@ -79,12 +79,22 @@ _SIGNATURES = {
         "snk_moe_sort": [P, P, P, P, I, I, P],
         "snk_norm_route_sort": [P, P, P, I, P, I, F, P, P, P, I, P, I, P, P, P, P, P, P, I, I, I, I, F, I, P, P],
         "snk_moe_combine": [P, P, P, P, I, I, I, P],
+        "snk_moe_scaled_rows": [P, P, P, P, P, I, I, I, I, P],
     },
     "sublayer": {
         "snk_norm_add": [P, P, P, I, P, I, I, F, I, P],
         "snk_cast_rows": [P, P, LL, I, P],
         "snk_gated_act": [P, P, I, I, I, I, I, P],
         "snk_head_norm_gate": [P, I, I, F, P, I, P, I, LL, P, I, I, I, F, F, I, P],
+        "snk_act_rows": [P, P, LL, I, I, P],
+        "snk_rms_cols": [P, LL, I, P, I, P, I, I, F, I, P],
+        "snk_add_dyt": [P, P, P, P, P, P, I, P, P, P, I, P, P, I, I, I, P],
+    },
+    "attention_latent": {
+        "snk_latent_prepare": [P, LL, I, P, LL, I, P, I, F, P, I, P, P, P, I, I, P, P, P, I, I, I, I, I, I, I, P],
+        "snk_latent_attention_tile_rows": [I],
+        "snk_latent_attention": [P, P, P, P, I, I, P, P, P, I, I, P, I, I, I, I, I, F, P, I, I, P, I, P],
+        "snk_heads_to_rows": [P, P, I, I, I, I, P],
     },
     "attention_split": {
         "snk_split_prepare": [P, LL, I, I, I, P, P, I, I, F, P, I, F, P, P, P, I, I, P, P, P, I, I, I, I, I, I, I, I, P],
@@ -252,6 +262,21 @@ class ExpertSum:
         return moe_combine(self.y, self.pair_pos, self.weights)
 
 
+class DeltaSum:
+    """A residual delta that is the sum of two sublayers' outputs (a layer whose mixer and feed-forward
+    read the same normalised input): ``a`` a float tensor [M, H], ``b`` a float tensor or an ``ExpertSum``.
+    A norm that knows it adds both into the residual itself; ``dense()`` forms the sum for anyone else."""
+
+    def __init__(self, a, b):
+        self.a, self.b = a, b
+        self.shape = tuple(a.shape)
+
+    def dense(self) -> torch.Tensor:
+        out = self.a.clone()
+        residual_add(out, self.b.dense() if isinstance(self.b, ExpertSum) else self.b)
+        return out
+
+
 def add_rmsnorm(residual: torch.Tensor, delta, gamma: torch.Tensor, eps: float,
                 dtype: torch.dtype, rows: torch.Tensor | None = None,
                 out: torch.Tensor | None = None) -> torch.Tensor:
@@ -261,6 +286,8 @@ def add_rmsnorm(residual: torch.Tensor, delta, gamma: torch.Tensor, eps: float,
     M, H = residual.shape
     _chk(residual, "residual", torch.float32)
     moe = None
+    if isinstance(delta, DeltaSum):
+        delta = delta.dense()
     if isinstance(delta, ExpertSum):
         if H % 4 == 0:
             moe, delta = delta, None
@@ -1046,7 +1073,7 @@ def sample(logits, temperature, top_k, top_p, uniform, out=None):
 
 # --- layers with norms on the sublayers' outputs; gated heads ---------------------------
 
-ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2}
+ACTIVATIONS = {"silu": 0, "relu": 1, "gelu_tanh": 2, "relu2": 3}
 
 
 def norm_add(residual, y, gamma, eps, dtype, x_out=None, want_x=True):
@@ -1125,6 +1152,219 @@ def head_norm_gate(a, heads, dv, eps, dtype, *, second=0, lam=0.0, weight=None, 
     check(fn("snk_head_norm_gate")(_ptr(a), stride, int(second), float(lam), _ptr(weight), w32, g_ptr, g32, g_ld,
                                    _ptr(out), M, heads, dv, float(eps), float(mult), code_of(dtype), _stream()),
           "head_norm_gate", work=lambda: (_nbytes(a, out) + M * heads * dv * (gate.element_size() if gate is not None else 0), 0))
+    return out
+
+
+def act_rows(x, activation: str, out=None):
+    """``act(x)`` elementwise in x's dtype, ``activation`` one of silu, relu, gelu_tanh, relu2 (the square
+    of relu); evaluated in float, rounded once at the store."""
+    _chk(x, "activation input", (torch.float32, torch.bfloat16))
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"activation {activation!r} (known: {', '.join(ACTIVATIONS)})")
+    if out is None:
+        out = torch.empty_like(x)
+    _chk(out, "activation output", x.dtype, x.shape)
+    check(fn("snk_act_rows")(_ptr(x), _ptr(out), x.numel(), ACTIVATIONS[activation], code_of(x.dtype), _stream()),
+          "act_rows", work=lambda: (_nbytes(x, out), 0))
+    return out
+
+
+def rms_cols(x, off: int, n: int, weight, eps: float, out=None):
+    """Columns [off, off + n) of every row of ``x`` [M, width] divided by their root mean square
+    (eps inside the root) and multiplied by ``weight`` [n]; statistics in float; [M, n] in x's dtype."""
+    _chk(x, "rms input", (torch.float32, torch.bfloat16))
+    M, width = x.shape
+    if off < 0 or off + n > width:
+        raise KernelError(f"columns [{off}, {off + n}) of a matrix of width {width}")
+    w32 = _small(weight, "rms weight", x.dtype)
+    _chk(weight, "rms weight", shape=(n,))
+    if out is None:
+        out = torch.empty(M, n, dtype=x.dtype, device=x.device)
+    _chk(out, "rms output", x.dtype, (M, n))
+    check(fn("snk_rms_cols")(_ptr(x), width, int(off), _ptr(weight), w32, _ptr(out), M, int(n), float(eps),
+                             code_of(x.dtype), _stream()), "rms_cols",
+          work=lambda: (2 * M * n * x.element_size(), 0))
+    return out
+
+
+def add_dyt(residual, delta, weight, bias, alpha, dtype, rows=None, out=None):
+    """``residual += delta`` (None, a float tensor, an ``ExpertSum`` or a ``DeltaSum``: its two parts are
+    summed first, then added), then the Dynamic Tanh norm ``tanh(alpha * x) * weight + bias`` of the sum in
+    the compute dtype.  With ``rows`` only those rows come out and the residual stays as it is."""
+    M, H = residual.shape
+    _chk(residual, "residual", torch.float32)
+    da = db = moe = None
+    if isinstance(delta, DeltaSum):
+        da, db = delta.a, delta.b
+    elif delta is not None:
+        da = delta
+    if isinstance(da, ExpertSum):
+        da, db = db, da
+    if isinstance(db, ExpertSum):
+        moe, db = db, None
+        _chk(moe.y, "expert outputs", torch.float32)
+        _chk(moe.pair_pos, "pair positions", torch.int32, (M * moe.weights.shape[1],))
+        _chk(moe.weights, "top-k weights", torch.float32)
+    for d in (da, db):
+        if d is not None:
+            _chk(d, "residual delta", torch.float32, (M, H))
+    s32 = _small(weight, "norm weight", dtype)
+    if _small(bias, "norm bias", dtype) != s32 or _small(alpha, "norm alpha", dtype) != s32:
+        raise KernelError("the norm's weight, bias and alpha must share a dtype")
+    _chk(weight, "norm weight", shape=(H,))
+    _chk(bias, "norm bias", shape=(H,))
+    if alpha.numel() != 1:
+        raise KernelError("the norm's alpha is one number")
+    R = M if rows is None else rows.numel()
+    if rows is not None:
+        _chk(rows, "norm rows", torch.int32)
+    if out is None:
+        out = torch.empty(R, H, dtype=dtype, device=residual.device)
+    _chk(out, "norm output", dtype, (R, H))
+    k = moe.weights.shape[1] if moe else 0
+    check(fn("snk_add_dyt")(_ptr(residual), _ptr(da), _ptr(db), _ptr(moe.y if moe else None),
+                            _ptr(moe.pair_pos if moe else None), _ptr(moe.weights if moe else None), k, _ptr(weight),
+                            _ptr(bias), _ptr(alpha), s32, _ptr(out), _ptr(rows), R, H, code_of(dtype), _stream()),
+          "add_dyt", work=lambda: (R * H * 4 * (1 + (rows is None and delta is not None) + (da is not None)
+                                                + (db is not None) + k) + _nbytes(out), 0))
+    return out
+
+
+def moe_scaled_rows(x, sorted_pair, weights, top_k: int):
+    """Rows for experts whose weight multiplies their input: (xs [pairs, K] with xs[r] = x[pair // k] *
+    weights.flat[pair], pair = sorted_pair[r], in x's dtype; ones float [M, k])."""
+    _chk(x, "expert input", (torch.float32, torch.bfloat16))
+    _chk(sorted_pair, "sorted pairs", torch.int32)
+    _chk(weights, "top-k weights", torch.float32)
+    R, K = sorted_pair.numel(), x.shape[1]
+    out = torch.empty(R, K, dtype=x.dtype, device=x.device)
+    ones = torch.empty_like(weights)
+    check(fn("snk_moe_scaled_rows")(_ptr(x), _ptr(sorted_pair), _ptr(weights), _ptr(out), _ptr(ones), R, K,
+                                    int(top_k), code_of(x.dtype), _stream()), "moe_scaled_rows",
+          work=lambda: (2 * _nbytes(out), 0))
+    return out, ones
+
+
+# --- latent attention -----------------------------------------------------------------------------
+
+LATENT_ATTENTION_CHUNK = 256
+
+
+def latent_prepare(q, q_off, kv, kv_off, c_gamma, eps, inv_freq, rot, positions, row_seg, block_table, page_size,
+                   pool, H, dim, rd, r, write_kv=True):
+    """The step's rows of a latent attention layer.  ``q`` [M, *] holds head h at column ``q_off`` + h *
+    (dim + rd) as [dim unrotated, rd rotated]; ``kv`` [M, *] holds [r latent, rd shared rotated key part] at
+    column ``kv_off`` (ignored without ``write_kv``).  The latent is divided by its root mean square and
+    multiplied by ``c_gamma``; the first ``rot`` elements of every rotated part turn in pairs (2i, 2i+1) by
+    position * inv_freq[i]; the row [r + rd] goes into its page of ``pool`` [pages, 1, page_size, r + rd].
+    Returns (q_unrot [H, M, dim] head-major, q_rot [M, H, rd])."""
+    dtype = q.dtype
+    _chk(q, "queries", (torch.float32, torch.bfloat16))
+    M = q.shape[0]
+    if q.shape[1] < q_off + H * (dim + rd):
+        raise KernelError(f"queries of width {q.shape[1]} hold no {H} heads of {dim + rd} from column {q_off}")
+    g32 = 0
+    if write_kv:
+        _chk(kv, "latent projection", dtype)
+        if kv.shape[0] != M or kv.shape[1] < kv_off + r + rd:
+            raise KernelError(f"latent projection {tuple(kv.shape)} holds no {r + rd} columns from {kv_off}")
+        g32 = _small(c_gamma, "latent norm weight", dtype)
+        _chk(c_gamma, "latent norm weight", shape=(r,))
+        _chk(pool, "latent pool", dtype)
+        if tuple(pool.shape[1:]) != (1, page_size, r + rd):
+            raise KernelError(f"latent pool {tuple(pool.shape)}, want [pages, 1, {page_size}, {r + rd}]")
+    rot = int(rot) if inv_freq is not None else 0
+    if rot:
+        _chk(inv_freq, "inv_freq", torch.float32, (rot // 2,))
+    _chk(positions, "positions", torch.int32, (M,))
+    _chk(row_seg, "row_seg", torch.int32, (M,))
+    _chk(block_table, "block table", torch.int32)
+    q_unrot = torch.empty(H, M, dim, dtype=dtype, device=q.device)
+    q_rot = torch.empty(M, H, rd, dtype=dtype, device=q.device)
+    check(fn("snk_latent_prepare")(
+        _ptr(q), q.shape[1], int(q_off), _ptr(kv if write_kv else None), kv.shape[1] if write_kv else 0, int(kv_off),
+        _ptr(c_gamma if write_kv else None), g32, float(eps), _ptr(inv_freq), rot, _ptr(positions), _ptr(row_seg),
+        _ptr(block_table), block_table.shape[1], page_size, _ptr(pool if write_kv else None), _ptr(q_unrot),
+        _ptr(q_rot), M, H, dim, rd, r, int(write_kv), code_of(dtype), _stream()), "latent_prepare",
+        work=lambda: ((2 * M * H * (dim + rd) + (2 * M * (r + rd) if write_kv else 0)) * q.element_size(), 0))
+    return q_unrot, q_rot
+
+
+def latent_attention_tile_rows(H: int) -> int:
+    """Rows of one request that a block of ``latent_attention`` serves beside each other for ``H`` heads."""
+    return int(fn("snk_latent_attention_tile_rows")(int(H)))
+
+
+def latent_attention(q_abs, q_rot, pool, block_table, page_size, positions, row_seg, scale, *, window=None,
+                     sink=None, tiles=None, tile_rows=1, out=None, num_chunks=1, scratch=None,
+                     chunk=LATENT_ATTENTION_CHUNK):
+    """Attention of all heads over one shared row per position: ``pool`` [pages, 1, page_size, r + rd] holds
+    [latent r, rotated key part rd]; head h's score is (q_abs[h, m] . latent + q_rot[m, h] . key part) *
+    scale, its value the latent.  ``q_abs`` [H, M, r] (head-major), ``q_rot`` [M, H, rd].  Causal, or with
+    ``window`` the last ``window`` keys; ``sink`` float [H]: exp(sink[h]) joins the softmax's denominator.
+    ``tiles`` int32 [n, 2] = (first row, rows <= tile_rows) of consecutive rows of one request covering the
+    step, None: every row alone.  ``num_chunks`` > 1 (rows alone only): keys in chunks of ``chunk`` at
+    absolute positions, merged in chunk order.  Returns the heads' weighted sums of the latent, [M, H, r]."""
+    H, M, r = q_abs.shape
+    rd = q_rot.shape[2]
+    dtype = q_abs.dtype
+    _chk(q_abs, "absorbed queries", (torch.float32, torch.bfloat16))
+    _chk(q_rot, "rotated queries", dtype, (M, H, rd))
+    _chk(pool, "latent pool", dtype)
+    if pool.dim() != 4 or tuple(pool.shape[1:]) != (1, page_size, r + rd):
+        raise KernelError(f"latent pool {tuple(pool.shape)}, want [pages, 1, {page_size}, {r + rd}]")
+    _chk(positions, "positions", torch.int32, (M,))
+    _chk(row_seg, "row_seg", torch.int32, (M,))
+    _chk(block_table, "block table", torch.int32)
+    if sink is not None:
+        _chk(sink, "sink", torch.float32, (H,))
+    n_tiles = M
+    if tiles is not None:
+        _chk(tiles, "attention tiles", torch.int32)
+        if tiles.dim() != 2 or tiles.shape[1] != 2:
+            raise KernelError("attention tiles must be [n, 2]")
+        n_tiles = tiles.shape[0]
+    if out is None:
+        out = torch.empty(M, H, r, dtype=dtype, device=q_abs.device)
+    _chk(out, "attention output", dtype, (M, H, r))
+    num_chunks = int(num_chunks)
+    if num_chunks > 1:
+        if tiles is not None:
+            raise KernelError("keys are cut into chunks for rows that stand alone only")
+        need = attention_scratch_bytes(M, H, r, num_chunks)
+        if scratch is None:
+            scratch = torch.empty(need, dtype=torch.uint8, device=q_abs.device)
+        _chk(scratch, "attention scratch", torch.uint8)
+        if scratch.numel() < need:
+            raise KernelError(f"attention scratch holds {scratch.numel()} bytes, needs {need}")
+
+    def work():
+        pos = positions.cpu().long()
+        keys = (pos + 1).clamp(max=int(window)) if window else pos + 1
+        total = int(keys.sum())
+        groups = -(-H // 16)
+        return (-(-total // max(tile_rows, 1)) * groups * (r + rd) * pool.element_size() + _nbytes(q_abs, q_rot, out),
+                2 * H * (2 * r + rd) * total)
+    check(fn("snk_latent_attention")(
+        _ptr(q_abs), _ptr(q_rot), _ptr(pool), _ptr(block_table), block_table.shape[1], page_size, _ptr(positions),
+        _ptr(row_seg), _ptr(tiles), n_tiles, int(tile_rows), _ptr(out), M, H, r, rd, int(window or 0), float(scale),
+        _ptr(sink), int(chunk), num_chunks, _ptr(scratch), code_of(dtype), _stream()), "latent_attention", work=work)
+    if num_chunks > 1:
+        check(fn("snk_attention_merge")(_ptr(scratch), _ptr(positions), _ptr(out), M, H, r, int(window or 0),
+                                        int(chunk), num_chunks, code_of(dtype), c_void_p(0), _stream()),
+              "attention_merge", work=lambda: (M * H * (r + 2) * 4 * num_chunks + _nbytes(out), 0))
+    return out
+
+
+def heads_to_rows(x, out=None):
+    """[H, M, d] (head-major) -> [M, H * d]."""
+    _chk(x, "head-major values", (torch.float32, torch.bfloat16))
+    H, M, d = x.shape
+    if out is None:
+        out = torch.empty(M, H * d, dtype=x.dtype, device=x.device)
+    _chk(out, "row-major values", x.dtype, (M, H * d))
+    check(fn("snk_heads_to_rows")(_ptr(x), _ptr(out), M, H, d, code_of(x.dtype), _stream()), "heads_to_rows",
+          work=lambda: (2 * _nbytes(x), 0))
     return out
 
 

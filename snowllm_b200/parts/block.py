@@ -5,7 +5,10 @@ The float residual sum is fused into the norm that follows it, so a block takes 
 previous block left and returns its own last delta; the model adds the final one.
 
 ``output_norm``: x += norm(mixer(x)); x += norm(ffn(x)).  The sums are made at once (nothing is left for
-the next block), and the block hands on the stream's copy in the compute dtype."""
+the next block), and the block hands on the stream's copy in the compute dtype.
+
+``parallel``: h = norm(x); x += mixer(h) + ffn(h).  One norm, both sublayers read its output; the sum of
+their outputs is left to the norm that follows (``kernels.DeltaSum``)."""
 from __future__ import annotations
 
 from ..ops import kernels
@@ -88,5 +91,40 @@ class OutputNormBlock:
         return None
 
 
+class ParallelBlock:
+    """h = norm(x); x += mixer(h) + ffn(h): the layer has ONE norm and both sublayers read its output.  The
+    block leaves the two outputs as a ``kernels.DeltaSum``: the next norm forms a + b, adds it into the float
+    residual and normalises in one kernel.  A layer may have the mixer alone."""
+    single_norm = True         # the model builds it without a second norm
+
+    def __init__(self, mixer, ffn, mixer_norm, ffn_norm=None):
+        if ffn_norm is not None:
+            raise ValueError("a parallel layer has one norm")
+        self.mixer, self.ffn, self.mixer_norm, self.ffn_norm = mixer, ffn, mixer_norm, None
+        self._names = tuple(f"{what}:{type(part).__name__}" for what, part in
+                            (("norm", mixer_norm), ("mixer", mixer), ("ffn", ffn)))
+
+    def parts(self):
+        return tuple(p for p in (self.mixer_norm, self.mixer, self.ffn) if p is not None)
+
+    def forward(self, ctx, residual, delta, cache, owns_cache=True):
+        with span(self._names[0]):
+            x = self.mixer_norm.forward(ctx, residual, delta)
+        ctx.tap("mixer_in", x)
+        with span(self._names[1]):
+            out = self.mixer.forward(ctx, x, cache, owns_cache)
+        ctx.tap("mixer_out", out)
+        if self.ffn is not None:
+            ctx.tap("ffn_in", x)
+            with span(self._names[2]):
+                f = self.ffn.forward(ctx, x)
+            ctx.tap("ffn_out", f)
+            out = kernels.DeltaSum(out, f)
+        if ctx.taps is not None:
+            ctx.tap("layer_out", residual + (out.dense() if hasattr(out, "dense") else out))
+        return out
+
+
 register_block("prenorm", PreNormBlock)
+register_block("parallel", ParallelBlock)
 register_block("output_norm", OutputNormBlock)

@@ -54,5 +54,30 @@ class GatedFFN(SwiGLU):
         return linear(act, self.w2, out_dtype=torch.float32)
 
 
+class MLP(Part):
+    """down(act(up x)) without a gate, ``activation`` one of silu, relu, gelu_tanh, relu2 (the square of
+    relu).  The activation is evaluated in float on the up product's output and rounded once."""
+    libraries = ("gemm", "gemm_skinny", "gemm_tc", "gemm_tc2", "sublayer")
+
+    def __init__(self, dtype, names, *, hidden_size: int, intermediate_size: int, activation: str = "relu2"):
+        super().__init__(dtype, names)
+        if activation not in kernels.ACTIVATIONS:
+            raise ConfigError(f"activation {activation!r} (known: {', '.join(kernels.ACTIVATIONS)})")
+        self.hidden_size, self.intermediate_size, self.activation = hidden_size, intermediate_size, activation
+        self.w1 = self.w2 = None
+
+    def declare(self, has):
+        H, I = self.hidden_size, self.intermediate_size
+        return [TensorSpec("up", self.names["up"], (I, H)), TensorSpec("down", self.names["down"], (H, I))]
+
+    def bind(self, tensors):
+        self.w1, self.w2 = tensors["up"], tensors["down"]
+
+    def forward(self, ctx, x):
+        u = linear(x, self.w1)
+        return linear(kernels.act_rows(u, self.activation), self.w2, out_dtype=torch.float32)
+
+
 register_ffn("swiglu", SwiGLU)
+register_ffn("mlp", MLP)
 register_ffn("gated", GatedFFN)

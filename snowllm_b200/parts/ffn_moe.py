@@ -19,12 +19,16 @@ class SigmoidMoE(Part):
     libraries = ("gemm", "gemm_skinny", "gemm_tc", "gemm_tc2", "moe", "elementwise")
 
     def __init__(self, dtype, names, *, hidden_size: int, intermediate_size: int, num_experts: int,
-                 top_k: int, norm_topk_prob: bool, use_expert_bias: bool, routed_scaling_factor: float):
+                 top_k: int, norm_topk_prob: bool, use_expert_bias: bool, routed_scaling_factor: float,
+                 scale_input: bool = False):
+        """``scale_input``: a pick's weight multiplies the expert's INPUT (the output is the plain sum of
+        expert(w * x) over the picks) instead of its output."""
         super().__init__(dtype, names)
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.num_experts, self.top_k = num_experts, top_k
         self.norm_topk_prob, self.use_expert_bias = norm_topk_prob, use_expert_bias
         self.routed_scaling_factor = routed_scaling_factor
+        self.scale_input = scale_input
         self.router = self.bias = self.w13 = self.w2 = None
         self._fused = False
         self._ticket = None            # the counter of the one-launch front end (zero between launches)
@@ -80,7 +84,7 @@ class SigmoidMoE(Part):
         weight, eps = getattr(norm, "weight", None), getattr(norm, "eps", None)
         if getattr(norm, "fusable_rms", False) is not True or weight is None or eps is None:
             return None
-        if not kernels.FUSE_ROUTER or not kernels.norm_route_sort_ok(residual, delta, weight, self.router, self.top_k):
+        if self.scale_input or not kernels.FUSE_ROUTER or not kernels.norm_route_sort_ok(residual, delta, weight, self.router, self.top_k):
             return None
         if self._ticket is None or self._ticket.device != residual.device:
             self._ticket = torch.zeros(1, dtype=torch.int32, device=residual.device)
@@ -101,6 +105,12 @@ class SigmoidMoE(Part):
             ctx.tap("moe_route", ids)
             ctx.tap("moe_route_input", x)
         cap = min(M, M * k)          # an expert gets a token at most once
+        if self.scale_input:
+            # the rows in expert order, each times its pick's weight; the outputs are then summed as they are
+            xs, weights = kernels.moe_scaled_rows(x, sorted_pair, weights, k)
+            act = grouped_linear_swiglu(xs, self.w13, offsets, M * k, cap, None, 1, self.interleaved)
+            y = grouped_linear(act, self.w2, offsets, M * k, cap, out_dtype=torch.float32)
+            return kernels.ExpertSum(y, pair_pos, weights)
         act = grouped_linear_swiglu(x, self.w13, offsets, M * k, cap, sorted_pair, k, self.interleaved)
         y = grouped_linear(act, self.w2, offsets, M * k, cap, out_dtype=torch.float32)
         return kernels.ExpertSum(y, pair_pos, weights)     # the norm that follows adds it into the residual

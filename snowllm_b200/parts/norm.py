@@ -1,11 +1,12 @@
-"""RMSNorm over the hidden size, fused with the residual sum that precedes it
-(snowllm/ops/norm.py:11-30; snowllm/models/lfm2/layers.py:99-104)."""
+"""Norms over the hidden size, fused with the residual sum that precedes them: RMSNorm
+(snowllm/ops/norm.py:11-30; snowllm/models/lfm2/layers.py:99-104) and Dynamic Tanh, which computes no
+statistics at all: tanh(alpha * x) * weight + bias with one learned number alpha."""
 from __future__ import annotations
 
 from ..ops import kernels
 from .base import Part
 from .registry import register_norm
-from .spec import INIT_ONES, KEEP_SMALL, TensorSpec
+from .spec import INIT_BIAS, INIT_ONES, KEEP_SMALL, TensorSpec
 
 
 class RMSNorm(Part):
@@ -37,4 +38,32 @@ class RMSNorm(Part):
         return residual if same else x
 
 
+class DynamicTanh(Part):
+    """tanh(alpha * x) * weight + bias, elementwise, in float: no mean, no variance, no eps.  Tensors:
+    ``weight`` [size], ``bias`` [size], ``alpha`` (one number)."""
+    libraries = ("sublayer",)
+    fusable_rms = False
+
+    def __init__(self, dtype, names, *, size: int):
+        super().__init__(dtype, names)
+        self.size = size
+        self.weight = self.bias = self.alpha = None
+
+    def declare(self, has):
+        n = self.names
+        return [TensorSpec("weight", n["weight"], (self.size,), INIT_ONES, KEEP_SMALL),
+                TensorSpec("bias", n["bias"], (self.size,), INIT_BIAS, KEEP_SMALL),
+                TensorSpec("alpha", n["alpha"], (), INIT_ONES, KEEP_SMALL)]
+
+    def bind(self, tensors):
+        self.weight, self.bias, self.alpha = tensors["weight"], tensors["bias"], tensors["alpha"]
+
+    def forward(self, ctx, residual, delta=None, rows=None):
+        """``residual += delta`` in float (a tensor, an ``ExpertSum`` or the ``DeltaSum`` of a layer whose
+        two sublayers ran side by side), then the norm of the sum in the compute dtype.  With ``rows`` only
+        those rows come out and the residual stays untouched."""
+        return kernels.add_dyt(residual, delta, self.weight, self.bias, self.alpha, self.dtype, rows=rows)
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("dyt", DynamicTanh)

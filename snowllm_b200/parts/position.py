@@ -26,6 +26,28 @@ class RotaryPosition:
         return self._inv_freq, self.rot_dim
 
 
+class PairedRotaryPosition:
+    """Rotary positions in the interleaved layout: element 2i turns with element 2i + 1 (not with the one
+    half a head away), f_i = theta^(-2i/rot_dim).  The table is worked out in double precision on the host
+    and kept in float; a kernel that rotates pairs asks for it (``layout``)."""
+    layout = "pairs"
+
+    def __init__(self, *, head_dim: int, theta: float, rot_dim: int | None = None):
+        self.head_dim, self.theta = head_dim, float(theta)
+        self.rot_dim = head_dim if rot_dim is None else rot_dim
+        if self.rot_dim % 2 or self.rot_dim > head_dim:
+            raise ValueError(f"rot_dim={self.rot_dim} must be even and at most head_dim={head_dim}")
+        self._inv_freq = None
+
+    def frequencies(self) -> list:
+        return [self.theta ** (-2.0 * i / self.rot_dim) for i in range(self.rot_dim // 2)]
+
+    def rotary(self, device):
+        if self._inv_freq is None or self._inv_freq.device != torch.device(device):
+            self._inv_freq = torch.tensor(self.frequencies(), dtype=torch.float64).to(torch.float32).to(device)
+        return self._inv_freq, self.rot_dim
+
+
 class YarnRotaryPosition:
     """Rotary frequencies stretched for contexts longer than the ``original`` one (YaRN).  With
     f_i = theta^(-2i/rot_dim) and place(t) = rot_dim * ln(original / (2 pi t)) / (2 ln theta), the
@@ -80,3 +102,4 @@ class NoPosition:
 register_position("rope", RotaryPosition)
 register_position("none", NoPosition)
 register_position("yarn", YarnRotaryPosition)
+register_position("rope_pairs", PairedRotaryPosition)
