@@ -15,7 +15,8 @@ computes does not depend on how its sequence was cut.
 Options, each a constructor parameter: ``q_rank`` (the query goes through a normalised latent of its own:
 q = W_uq rmsnorm(W_dq x)), ``window`` (the last ``window`` keys; None: causal), ``sink`` (a learned number per
 head whose exponential joins the softmax's denominator), ``reads_cache`` (no W_dkv: the layer attends over
-the rows another layer cached).  ``cache_window`` is how many positions the owner of the cache keeps."""
+the rows another layer cached).  ``cache_window`` is how many positions the owner of the cache keeps (None:
+all of them; by default the layer's own window)."""
 from __future__ import annotations
 
 import torch
@@ -34,7 +35,7 @@ class LatentAttention(Part):
 
     def __init__(self, dtype, names, *, hidden_size: int, num_heads: int, head_dim: int, rot_dim: int,
                  v_head_dim: int, kv_rank: int, scale: float, norm_eps: float, position: dict,
-                 q_rank: int | None = None, window: int | None = None, cache_window: int | None = None,
+                 q_rank: int | None = None, window: int | None = None, cache_window="own",
                  sink: bool = False, reads_cache: bool = False):
         super().__init__(dtype, names)
         if kv_rank > 512:
@@ -43,8 +44,10 @@ class LatentAttention(Part):
         self.v_head_dim, self.kv_rank, self.q_rank = v_head_dim, kv_rank, q_rank
         self.scale, self.norm_eps, self.window, self.sink_on = float(scale), float(norm_eps), window, bool(sink)
         self.reads_cache = reads_cache
-        self.cache_window = cache_window if cache_window is not None or window is None else window
-        if window is None and cache_window is not None:
+        # how many positions the cache keeps: "own" this layer's window; None every position (a reader of
+        # these rows may see further than the layer that writes them)
+        self.cache_window = window if cache_window == "own" else cache_window
+        if window is None and self.cache_window is not None:
             raise ConfigError("a layer that sees every key cannot live on a cache that keeps a window")
         if window is not None and self.cache_window is not None and self.cache_window < window:
             raise ConfigError(f"cache_window={cache_window} is shorter than the layer's window {window}")

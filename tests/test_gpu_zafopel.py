@@ -177,9 +177,10 @@ def test_attention_kernel_finds_a_far_key_and_counts_the_sink_once(dtype, mode):
     T, H, r, rd, P = 300, 4, 40, 4, 8
     q = torch.randn(T, H, r + rd, generator=g).to(dtype)
     rows = (torch.randn(T, r + rd, generator=g) * 0.2).to(dtype)
-    rows[3, r:] = (q[T - 1, 0, r:].float() * 30).to(dtype)
+    looks = q[T - 1, 0, r:].float()
+    rows[3, r:] = (looks * (100 / float(looks @ looks))).to(dtype)         # a score of 30 after the scale
     rows[3, :r] = 1.5
-    sink = torch.tensor([-30.0, 40.0, -40.0, 0.5])
+    sink = torch.tensor([-30.0, 200.0, -200.0, 0.5])
     pool, table = paged(rows, P, dtype, g)
     got = run_kernel(q, pool, table, P, r, 0.3, None, sink, mode).float().cpu().double()
     want = plain_shared_row_attention(q.double(), rows.double(), r, 0.3, None, sink.double())
