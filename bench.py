@@ -1,7 +1,7 @@
 """Decode and prefill throughput of the engine at the layer sizes of the LFM2.5 models, random weights.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--config 8b-a1b|dense-1.2b|dense-2.6b]
-    python bench.py --design beledra        (another design beside dense LFM2 at equal size; one JSON line)
+    python bench.py --design beledra|zafopel   (another design beside the closest existing model at equal size; one JSON line)
                     [--batch B] [--context C] [--dtype bfloat16|float32] [--impl ours|reference]
 
 Prints ONE JSON line.  Without flags: LFM2.5-8B-A1B sizes, 8 requests at context 8,192.
@@ -121,13 +121,57 @@ def _lfm2_like(width: int, layers: int, ff: int, vocab: int = 65536) -> dict:
             "max_position_embeddings": 128000, "intermediate_size": ff}
 
 
+def _zafopel(width: int, layers: int, ff: int, vocab: int = 65536) -> dict:
+    """Zafopel at sizes that resemble a real model's layers: heads of 128 + 64 rotated dimensions over a latent
+    of 512; per four layers three with queries through a latent, causal, with sinks, and one with a window of
+    2,048 (every second of those reads the rows the one before it cached); the first layer's feed-forward is
+    dense, the others route every token to 4 of 32 experts of ff/8."""
+    heads = width // 128
+    common = {"heads": heads, "dim": 128, "rot_dim": 64, "vdim": 128, "kv_rank": 512, "scale": 192 ** -0.5}
+    routed = {"kind": "moe", "expert": {"ff": ff // 8}, "router": {"experts": 32, "top": 4}}
+    out, last_window = [], None
+    for i in range(layers):
+        mlp = {"kind": "dense", "ff": ff} if i == 0 else routed
+        if i % 4 == 1:
+            mixer = dict(common, mask={"size": 2048}, rot={"dims": 64, "base": 250000.0})
+            if last_window is not None:
+                mixer["kv_from"], last_window = last_window, None
+            else:
+                last_window = i
+            out.append({"type": "latent_attention", "mixer": mixer, "mlp": mlp})
+        else:
+            out.append({"type": "latent_attention_2", "mlp": mlp,
+                        "mixer": dict(common, q_rank=width // 2, rot={"dims": 64, "base": 10000.0})})
+    return {"architecture": "Zafopel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "layers": json.loads(json.dumps(out))}
+
+
+def _lfm2_moe_like(width: int, layers: int, ff: int, vocab: int = 65536) -> dict:
+    """The closest existing model at equal size: LFM2 with routed experts, attention in every layer, the same
+    width, depth, head count and head size, one dense layer first, then 4 of 32 experts of ff/8."""
+    heads = width // 128
+    return {"architectures": ["Lfm2MoeForCausalLM"], "model_type": "lfm2_moe", "vocab_size": vocab,
+            "hidden_size": width, "num_hidden_layers": layers, "layer_types": ["full_attention"] * layers,
+            "num_attention_heads": heads, "num_key_value_heads": max(heads // 4, 1), "conv_L_cache": 3,
+            "conv_bias": False, "rope_theta": 1000000.0, "norm_eps": 1e-5, "tie_word_embeddings": True,
+            "max_position_embeddings": 128000, "intermediate_size": ff, "num_dense_layers": 1, "num_experts": 32,
+            "num_experts_per_tok": 4, "moe_intermediate_size": ff // 8, "norm_topk_prob": True,
+            "use_expert_bias": True, "routed_scaling_factor": 1.0}
+
+
 DESIGN_SIZES = {"w2048-l12": (2048, 12, 8192), "w1024-l6": (1024, 6, 4096)}
+# design -> (its name, its configuration at a size, the closest existing model at that size, what that is)
+DESIGNS = {"beledra": ("Beledra", _beledra, ("lfm2_dense", _lfm2_like),
+                       "dense LFM2 at equal width, depth, feed-forward width and head counts"),
+           "zafopel": ("Zafopel", _zafopel, ("lfm2_moe", _lfm2_moe_like),
+                       "LFM2 with routed experts at equal width, depth, head count and size, expert count and width")}
 
 
 def design_compare(a) -> dict:
-    """``--design beledra``: prompt and decode throughput of the Beledra design at DESIGN_SIZES (seeded random
-    weights) beside dense LFM2 at equal size, each with its per-kernel table (time, bytes and flops from the
-    kernels' ledger, the fraction of the measured roofline)."""
+    """``--design NAME``: prompt and decode throughput of that design at DESIGN_SIZES (seeded random weights)
+    beside the closest existing model at equal size, each with its per-kernel table (time, bytes and flops
+    from the kernels' ledger, the fraction of the measured roofline)."""
+    name, ours, (other, theirs), beside = DESIGNS[a.design]
     import torch
 
     from snowllm_b200.config.engine import DEFAULT_PAGE_SIZE
@@ -144,7 +188,7 @@ def design_compare(a) -> dict:
         if a.layers:
             layers = min(layers, a.layers)
         models = {who: load_random(cfg, seed=0, dtype=a.dtype, device="cuda")
-                  for who, cfg in (("beledra", _beledra(width, layers, ff)), ("lfm2_dense", _lfm2_like(width, layers, ff)))}
+                  for who, cfg in ((a.design, ours(width, layers, ff)), (other, theirs(width, layers, ff)))}
         torch.cuda.synchronize()
         per = {who: {} for who in models}
         # the timed runs first (captured decode steps), the per-kernel tables afterwards, launch by launch:
@@ -166,7 +210,7 @@ def design_compare(a) -> dict:
         gc.collect()
         torch.cuda.empty_cache()
         sizes[label] = dict(width=width, layers=layers, ff=ff, **per)
-    return {"design": "Beledra", "beside": "dense LFM2 at equal width, depth, feed-forward width and head counts",
+    return {"design": name, "beside": beside,
             "dtype": a.dtype, "prefill_tokens": PREFILL_TOKENS, "decode_context": context, "page_size": page,
             "data": "synthetic: seeded random weights and uniform random token ids; cache filled with random values",
             "peaks": {"hbm_gbs": pk["hbm_gbs"], "bf16_tflops_sustained": pk["bf16_tflops_sustained"], "of": pk_source},
@@ -660,8 +704,9 @@ def main() -> int:
     ap.add_argument("--page-size", type=int, default=None)
     ap.add_argument("--enforce-eager", action="store_true", help="no CUDA graphs for the decode steps")
     ap.add_argument("--skip", default="", help="comma list of: e2e, prefill, points, kernels, mixed")
-    ap.add_argument("--design", default=None, choices=("beledra",),
-                    help="instead of the default workload: this design at a few sizes beside dense LFM2 at equal size")
+    ap.add_argument("--design", default=None, choices=tuple(DESIGNS),
+                    help="instead of the default workload: this design at a few sizes beside the closest existing "
+                         "model at equal size")
     a = ap.parse_args()
     if a.impl == "reference":
         print(json.dumps(reference_arm()))

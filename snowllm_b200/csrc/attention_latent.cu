@@ -13,7 +13,8 @@
 //                      denominator that has no key and no value); rows alone may have their keys cut into
 //                      chunks (merged in chunk order by attention.cu's merge; the sink enters in a row's
 //                      first chunk)
-//   latent_attention_mma: bfloat16 on mma.sync, see there
+//   latent_attention_mma: bfloat16 with r and rd multiples of 16, on mma.sync: what the entry point launches
+//                      for those sizes (see there)
 //   heads_to_rows:     [heads, M, d] -> [M, heads * d]
 //
 // Scores, softmax weights, maxima and sums are float whatever the cache dtype.  Key tiles are aligned to
@@ -302,10 +303,307 @@ __global__ void latent_attention_kernel(
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// bfloat16 on mma.sync (m16n8k16): a block of four warps serves 16 * MT (row, head) units over 64-key tiles
+// that come in by 16-byte cp.async, two stages.  Per tile: (1) S = Q K^T, each warp 16 of the tile's keys
+// over the whole row width (bfloat16 products are exact in float, float sums), scaled and left in shared
+// memory; (2) the softmax step in float, 128 / units threads per unit: mask, running maximum, weights and
+// their sum, the factor the sums so far shrink by; the float weights are split into two bfloat16 terms,
+// p = hi + lo with lo = bf16(p - hi), so that P keeps 16 mantissa bits; (3) O = O * factor + P V, each warp a
+// quarter of the value's columns (the value is the first r elements of the key row, read transposed by
+// ldmatrix) with both terms of P.  r and rd are multiples of 16.  A unit whose keys a tile does not touch
+// leaves the tile with its sums unchanged bit for bit, so a row's result does not depend on its neighbours.
+#define LM_KEYS 64
+#define LM_WARPS 4
+#define LM_S_STRIDE 68          // floats per row of S
+#define LM_P_STRIDE 144         // bytes per row of a P term: 64 keys of 2 bytes and 16 bytes of padding
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+// Four 8 x 8 matrices of 16-bit elements from shared memory, lane L giving the address of row L % 8 of matrix
+// L / 8.  Plain: a lane gets elements 2 (L % 4), + 1 of row L / 4 of each matrix; .trans: rows 2 (L % 4), + 1
+// of column L / 4.
+__device__ __forceinline__ void ldsm_x4(uint32_t (&r)[4], const void* row) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* row) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(row);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+
+// MT: tiles of 16 units; NT: tiles of 8 value columns per warp (4 * 8 * NT >= r).
+template <int MT, int NT>
+__global__ void __launch_bounds__(LM_WARPS * 32, 1) latent_attention_mma_kernel(
+    const bf16* __restrict__ q_abs, const bf16* __restrict__ q_rot, const bf16* __restrict__ pool,
+    const int* __restrict__ block_table, int max_pages, int page_size, const int* __restrict__ positions,
+    const int* __restrict__ row_seg, const int* __restrict__ tiles, bf16* __restrict__ out, int M, int H, int r,
+    int rd, int hpb, int window, float scale, const float* __restrict__ sink, int k_stride, int chunk,
+    int num_chunks, float* __restrict__ part_o, float* __restrict__ part_ml) {
+  pdl_begin();
+  extern __shared__ __align__(16) unsigned char lm_raw[];
+  constexpr int U = 16 * MT;                             // unit rows of the block
+  constexpr int TPU = LM_WARPS * 32 / U;                 // threads per unit in the softmax step
+  constexpr int KPT = LM_KEYS / TPU;                     // keys per such thread
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int m0 = tiles ? tiles[2 * blockIdx.x] : (int)blockIdx.x;
+  const int rows = tiles ? tiles[2 * blockIdx.x + 1] : 1;
+  const int h0 = blockIdx.y * hpb;
+  const int nh = min(hpb, H - h0);
+  const int units = rows * nh;
+  const int kw = r + rd;
+  const int pos0 = positions[m0];
+  int lo = window > 0 ? max(0, pos0 - window + 1) : 0;
+  int hi = pos0 + rows - 1;
+  bool first_chunk = true;
+  if (num_chunks > 1) {
+    const int cnk = lo / chunk + (int)blockIdx.z;
+    if ((long long)cnk * chunk > hi) return;
+    first_chunk = blockIdx.z == 0;
+    lo = max(lo, cnk * chunk);
+    hi = min(hi, (cnk + 1) * chunk - 1);
+  }
+  const int stage_bytes = LM_KEYS * k_stride;
+  unsigned char* qs = lm_raw + 2 * (size_t)stage_bytes;                  // [U][k_stride]
+  float* ss = reinterpret_cast<float*>(qs + (size_t)U * k_stride);        // [U][LM_S_STRIDE]
+  unsigned char* p_hi = reinterpret_cast<unsigned char*>(ss + U * LM_S_STRIDE);
+  unsigned char* p_lo = p_hi + U * LM_P_STRIDE;
+  float* m_s = reinterpret_cast<float*>(p_lo + U * LM_P_STRIDE);          // [U] running maximum
+  float* l_s = m_s + U;                                                   // [U] running sum
+  float* c_s = l_s + U;                                                   // [U] this tile's factor
+
+  // the units' queries: [absorbed r, rotated rd] per row, zeros for rows beyond the block's units
+  const int per = kw / 8;
+  for (int i = tid; i < U * per; i += LM_WARPS * 32) {
+    const int u = i / per, d = (i - u * per) * 8;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (u < units) {
+      const int rr = u / nh, h = h0 + (u - rr * nh);
+      const bf16* src = d < r ? q_abs + ((size_t)h * M + m0 + rr) * r + d
+                              : q_rot + ((size_t)(m0 + rr) * H + h) * rd + (d - r);
+      v = *reinterpret_cast<const uint4*>(src);
+    }
+    *reinterpret_cast<uint4*>(qs + (size_t)u * k_stride + d * 2) = v;
+  }
+  if (tid < U) {
+    const bool with_sink = sink && first_chunk && tid < units;
+    m_s[tid] = with_sink ? sink[h0 + tid % nh] : -INFINITY;
+    l_s[tid] = with_sink ? 1.f : 0.f;
+  }
+  const int* bt = block_table + (size_t)row_seg[m0] * max_pages;
+  const int t_first = (lo / LM_KEYS) * LM_KEYS;
+  const int ntiles = (hi - t_first) / LM_KEYS + 1;
+
+  auto issue = [&](int tile) {
+    if (tile < ntiles) {
+      const int t0 = t_first + tile * LM_KEYS;
+      unsigned char* ks = lm_raw + (size_t)(tile & 1) * stage_bytes;
+      for (int v = tid; v < LM_KEYS * per; v += LM_WARPS * 32) {
+        const int j = v / per, c = v - j * per;
+        const int kp = t0 + j;
+        const bool valid = kp >= lo && kp <= hi;
+        const bf16* src = pool;
+        if (valid) src = pool + ((size_t)bt[kp / page_size] * page_size + kp % page_size) * kw + c * 8;
+        la_cp_async16(ks + j * k_stride + c * 16, src, valid);
+      }
+    }
+    la_cp_async_commit();
+  };
+
+  float oacc[MT][NT][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) oacc[mt][nt][e] = 0.f;
+
+  // the softmax step's unit of this thread
+  const int su = tid / TPU, sub = tid % TPU;
+  const int s_p = pos0 + (su < units ? su / nh : 0);
+  const int col_w = warp * 8 * NT;                        // this warp's first value column
+
+  issue(0);
+  for (int tile = 0; tile < ntiles; ++tile) {
+    la_cp_async_wait<0>();
+    __syncthreads();                                     // the tile is in; the step before is over everywhere
+    issue(tile + 1);
+    const int t0 = t_first + tile * LM_KEYS;
+    const unsigned char* ks = lm_raw + (size_t)(tile & 1) * stage_bytes;
+
+    // (1) S = Q K^T for this warp's 16 keys
+    {
+      float sacc[MT][2][4];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) sacc[mt][n][e] = 0.f;
+      const unsigned char* k_at = ks + (size_t)(warp * 16 + (lane >> 4) * 8 + (lane & 7)) * k_stride + ((lane >> 3) & 1) * 16;
+      const unsigned char* q_at = qs + (size_t)(lane & 15) * k_stride + (lane >> 4) * 16;
+      for (int kk = 0; kk < kw / 16; ++kk) {
+        uint32_t bk[4];
+        ldsm_x4(bk, k_at + kk * 32);
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          uint32_t a[4];
+          ldsm_x4(a, q_at + (size_t)mt * 16 * k_stride + kk * 32);
+          mma_bf16_16816(sacc[mt][0], a, bk[0], bk[1]);
+          mma_bf16_16816(sacc[mt][1], a, bk[2], bk[3]);
+        }
+      }
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int n = 0; n < 2; ++n) {
+          float* at = ss + (mt * 16 + (lane >> 2)) * LM_S_STRIDE + warp * 16 + n * 8 + (lane & 3) * 2;
+          at[0] = sacc[mt][n][0] * scale;
+          at[1] = sacc[mt][n][1] * scale;
+          at[8 * LM_S_STRIDE] = sacc[mt][n][2] * scale;
+          at[8 * LM_S_STRIDE + 1] = sacc[mt][n][3] * scale;
+        }
+    }
+    __syncthreads();
+
+    // (2) the softmax step of unit su, TPU threads side by side
+    {
+      const int klo = max(lo, window > 0 ? s_p - window + 1 : 0);
+      const int khi = su < units ? min(s_p, hi) : -1;
+      float sv[KPT];
+      float mx = -INFINITY;
+#pragma unroll
+      for (int j = 0; j < KPT; ++j) {
+        const int kp = t0 + sub * KPT + j;
+        const bool valid = kp >= klo && kp <= khi;
+        sv[j] = valid ? ss[su * LM_S_STRIDE + sub * KPT + j] : -INFINITY;
+        mx = fmaxf(mx, sv[j]);
+      }
+#pragma unroll
+      for (int o = TPU / 2; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      const float m_old = m_s[su];
+      const float m_new = fmaxf(m_old, mx);
+      const float corr = m_new == -INFINITY ? 1.f : expf(m_old - m_new);
+      float sum = 0.f;
+      __nv_bfloat16* ph = reinterpret_cast<__nv_bfloat16*>(p_hi + su * LM_P_STRIDE) + sub * KPT;
+      __nv_bfloat16* pl = reinterpret_cast<__nv_bfloat16*>(p_lo + su * LM_P_STRIDE) + sub * KPT;
+#pragma unroll
+      for (int j = 0; j < KPT; ++j) {
+        const float pw = sv[j] == -INFINITY ? 0.f : expf(sv[j] - m_new);
+        sum += pw;
+        const __nv_bfloat16 hi16 = __float2bfloat16_rn(pw);
+        ph[j] = hi16;
+        pl[j] = __float2bfloat16_rn(pw - __bfloat162float(hi16));
+      }
+#pragma unroll
+      for (int o = TPU / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      __syncwarp();
+      if (sub == 0) {
+        m_s[su] = m_new;
+        l_s[su] = l_s[su] * corr + sum;
+        c_s[su] = corr;
+      }
+    }
+    __syncthreads();
+
+    // (3) O = O * factor + P V for this warp's columns
+    {
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        const float c_lo = c_s[mt * 16 + (lane >> 2)], c_hi = c_s[mt * 16 + (lane >> 2) + 8];
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          oacc[mt][nt][0] *= c_lo;
+          oacc[mt][nt][1] *= c_lo;
+          oacc[mt][nt][2] *= c_hi;
+          oacc[mt][nt][3] *= c_hi;
+        }
+      }
+      const unsigned char* v_at = ks + (size_t)(((lane >> 3) & 1) * 8 + (lane & 7)) * k_stride + (col_w + (lane >> 4) * 8) * 2;
+#pragma unroll
+      for (int kk = 0; kk < LM_KEYS / 16; ++kk) {
+        uint32_t a_hi[MT][4], a_lo[MT][4];
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          const size_t at = (size_t)(mt * 16 + (lane & 15)) * LM_P_STRIDE + kk * 32 + (lane >> 4) * 16;
+          ldsm_x4(a_hi[mt], p_hi + at);
+          ldsm_x4(a_lo[mt], p_lo + at);
+        }
+#pragma unroll
+        for (int np = 0; np < NT / 2; ++np) {
+          if (col_w + np * 16 >= r) break;                // columns beyond the value (the same for the whole warp)
+          uint32_t bv[4];
+          ldsm_x4_trans(bv, v_at + (size_t)kk * 16 * k_stride + np * 32);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            mma_bf16_16816(oacc[mt][2 * np], a_hi[mt], bv[0], bv[1]);
+            mma_bf16_16816(oacc[mt][2 * np], a_lo[mt], bv[0], bv[1]);
+            mma_bf16_16816(oacc[mt][2 * np + 1], a_hi[mt], bv[2], bv[3]);
+            mma_bf16_16816(oacc[mt][2 * np + 1], a_lo[mt], bv[2], bv[3]);
+          }
+        }
+      }
+    }
+  }
+  la_cp_async_wait<0>();
+  __syncthreads();
+
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int half = 0; half < 2; ++half) {
+      const int u = mt * 16 + (lane >> 2) + half * 8;
+      if (u >= units) continue;
+      const int rr = u / nh, h = h0 + (u - rr * nh);
+      if (num_chunks > 1) {
+        const size_t slot = ((size_t)blockIdx.x * H + h) * num_chunks + blockIdx.z;
+#pragma unroll
+        for (int nt = 0; nt < NT; ++nt) {
+          const int col = col_w + nt * 8 + (lane & 3) * 2;
+          if (col < r) {
+            part_o[slot * r + col] = oacc[mt][nt][half * 2];
+            part_o[slot * r + col + 1] = oacc[mt][nt][half * 2 + 1];
+          }
+        }
+        if (warp == 0 && (lane & 3) == 0) {
+          part_ml[slot * 2] = m_s[u];
+          part_ml[slot * 2 + 1] = l_s[u];
+        }
+        continue;
+      }
+      const float inv = 1.f / l_s[u];
+      bf16* dst = out + ((size_t)(m0 + rr) * H + h) * r;
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const int col = col_w + nt * 8 + (lane & 3) * 2;
+        if (col < r)
+          *reinterpret_cast<__nv_bfloat162*>(dst + col) =
+              __floats2bfloat162_rn(oacc[mt][nt][half * 2] * inv, oacc[mt][nt][half * 2 + 1] * inv);
+      }
+    }
+}
+
+// Whether the tensor-core kernel takes these sizes (bfloat16 only).  SNOWLLM_B200_LATENT_MMA=0 in the
+// environment keeps every launch on the CUDA-core kernel (for A/B runs and tests of that path).
+static inline bool lm_ok(int r, int rd, int dtype) {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("SNOWLLM_B200_LATENT_MMA");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on && dtype == SNK_BF16 && r % 16 == 0 && rd % 16 == 0 && r >= 16 && r <= 512;
+}
+static inline int lm_heads_per_block(int H) { return H < 32 ? H : 32; }
+
 // Heads a block takes, and the rows of one request it serves beside each other, for H heads.
 static inline int la_heads_per_block(int H) { return H < LA_UPW * LA_MAX_WARPS ? H : LA_UPW * LA_MAX_WARPS; }
-SNK_API int snk_latent_attention_tile_rows(int H) {
-  const int rows = (LA_UPW * LA_MAX_WARPS) / la_heads_per_block(H);
+SNK_API int snk_latent_attention_tile_rows(int H, int r, int rd, int dtype) {
+  const int rows = lm_ok(r, rd, dtype) ? 32 / lm_heads_per_block(H) : (LA_UPW * LA_MAX_WARPS) / la_heads_per_block(H);
   return rows < 1 ? 1 : rows;
 }
 
@@ -318,6 +616,48 @@ SNK_API int snk_latent_attention(const void* q_abs, const void* q_rot, const voi
   if (H <= 0 || r <= 0 || rd < 0 || r > 32 * 16) return SNK_ERR_SIZE;
   if (num_chunks < 1 || num_chunks > 65535 || chunk <= 0 || chunk % LA_TILE) return SNK_ERR_SIZE;
   if (num_chunks > 1 && (tiles != nullptr || scratch == nullptr)) return SNK_ERR_SIZE;
+  if (lm_ok(r, rd, dtype) && ((uintptr_t)pool % 16) == 0 && ((uintptr_t)q_abs % 16) == 0 &&
+      ((uintptr_t)q_rot % 16) == 0) {
+    if (chunk % LM_KEYS) return SNK_ERR_SIZE;
+    const int hpb = lm_heads_per_block(H);
+    if (tile_rows < 1 || (tiles && tile_rows * hpb > 32)) return SNK_ERR_SIZE;
+    const int units_max = (tiles ? tile_rows : 1) * hpb;
+    const int mt = units_max > 16 ? 2 : 1;
+    const int groups = (H + hpb - 1) / hpb;
+    if (groups > 65535) return SNK_ERR_SIZE;
+    const int kw = r + rd;
+    int k_stride = kw * 2 + 16;                          // a multiple of 32 bytes and 16: an odd number of 16-byte units
+    const int U = 16 * mt;
+    const size_t smem = 2 * (size_t)LM_KEYS * k_stride + (size_t)U * k_stride + (size_t)U * LM_S_STRIDE * 4 +
+                        2 * (size_t)U * LM_P_STRIDE + 3 * (size_t)U * 4;
+    if (smem > 227 * 1024) return SNK_ERR_SIZE;
+    float* part_o = static_cast<float*>(scratch);
+    float* part_ml = part_o ? part_o + (size_t)M * H * num_chunks * r : nullptr;
+    dim3 grid(n_tiles, groups, num_chunks);
+#define LM_LAUNCH(MT_, NT_)                                                                                     \
+  do {                                                                                                          \
+    if (smem > 48 * 1024)                                                                                       \
+      cudaFuncSetAttribute(latent_attention_mma_kernel<MT_, NT_>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+                           (int)smem);                                                                          \
+    snk_launch(latent_attention_mma_kernel<MT_, NT_>, dim3(grid), dim3(LM_WARPS * 32), smem, stream,            \
+               static_cast<const bf16*>(q_abs), static_cast<const bf16*>(q_rot), static_cast<const bf16*>(pool),\
+               block_table, max_pages, page_size, positions, row_seg, tiles, static_cast<bf16*>(out), M, H, r,  \
+               rd, hpb, window, scale, sink, k_stride, chunk, num_chunks, part_o, part_ml);                     \
+  } while (0)
+#define LM_PICK(MT_)                                   \
+  do {                                                 \
+    if (r <= 64) LM_LAUNCH(MT_, 2);                    \
+    else if (r <= 128) LM_LAUNCH(MT_, 4);              \
+    else if (r <= 256) LM_LAUNCH(MT_, 8);              \
+    else LM_LAUNCH(MT_, 16);                           \
+  } while (0)
+    if (mt == 2) LM_PICK(2);
+    else LM_PICK(1);
+#undef LM_PICK
+#undef LM_LAUNCH
+    SNK_LAUNCH_CHECK();
+    return 0;
+  }
   const int hpb = la_heads_per_block(H);
   if (tile_rows < 1 || tile_rows * hpb > LA_UPW * LA_MAX_WARPS) return SNK_ERR_SIZE;
   const int units_max = (tiles ? tile_rows : 1) * hpb;

@@ -92,7 +92,7 @@ _SIGNATURES = {
     },
     "attention_latent": {
         "snk_latent_prepare": [P, LL, I, P, LL, I, P, I, F, P, I, P, P, P, I, I, P, P, P, I, I, I, I, I, I, I, P],
-        "snk_latent_attention_tile_rows": [I],
+        "snk_latent_attention_tile_rows": [I, I, I, I],
         "snk_latent_attention": [P, P, P, P, I, I, P, P, P, I, I, P, I, I, I, I, I, F, P, I, I, P, I, P],
         "snk_heads_to_rows": [P, P, I, I, I, I, P],
     },
@@ -1290,9 +1290,11 @@ def latent_prepare(q, q_off, kv, kv_off, c_gamma, eps, inv_freq, rot, positions,
     return q_unrot, q_rot
 
 
-def latent_attention_tile_rows(H: int) -> int:
-    """Rows of one request that a block of ``latent_attention`` serves beside each other for ``H`` heads."""
-    return int(fn("snk_latent_attention_tile_rows")(int(H)))
+def latent_attention_tile_rows(H: int, r: int, rd: int, dtype) -> int:
+    """Rows of one request that a block of ``latent_attention`` serves beside each other for ``H`` heads over
+    rows of r + rd (bfloat16 with r and rd multiples of 16 runs on the tensor cores, 32 units a block; everything
+    else on the CUDA cores, 16 units)."""
+    return int(fn("snk_latent_attention_tile_rows")(int(H), int(r), int(rd), code_of(dtype)))
 
 
 def latent_attention(q_abs, q_rot, pool, block_table, page_size, positions, row_seg, scale, *, window=None,

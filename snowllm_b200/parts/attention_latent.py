@@ -143,7 +143,7 @@ class LatentAttention(Part):
         q_abs = grouped_linear(q_unrot.view(H * M, self.head_dim), self.w_ukT, offsets, H * M, M).view(H, M, r)
         ctx.tap("attention_q", (q_abs, q_rot))
         decode_only = max(ctx.host_seg_len) <= 1
-        tile_rows = 1 if decode_only else kernels.latent_attention_tile_rows(H)
+        tile_rows = 1 if decode_only else kernels.latent_attention_tile_rows(H, r, rd, self.dtype)
         num_chunks, scratch, chunk = 1, None, kernels.LATENT_ATTENTION_CHUNK
         if decode_only:
             # rows of decoded tokens: their keys in chunks, one block each, merged in chunk order

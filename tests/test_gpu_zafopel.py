@@ -133,23 +133,26 @@ def run_kernel(q, pool, table, P, r, scale, window, sink, mode, chunk=64):
     positions = torch.arange(T, dtype=torch.int32, device="cuda")
     kw = dict(window=window, sink=None if sink is None else sink.float().cuda())
     if mode == "tiles":
-        n = kernels.latent_attention_tile_rows(H)
+        n = kernels.latent_attention_tile_rows(H, r, q.shape[2] - r, q.dtype)
         tiles = torch.tensor([[s, min(n, T - s)] for s in range(0, T, n)], dtype=torch.int32, device="cuda")
         kw.update(tiles=tiles, tile_rows=n)
     if mode == "chunks":
-        lo = 0 if window is None else max(0, T - window)
-        kw.update(num_chunks=(T - 1) // chunk - lo // chunk + 1 if window else (T - 1) // chunk + 1, chunk=chunk)
+        # the most chunks any row spans
+        kw.update(num_chunks=min((window - 1) // chunk + 2, (T - 1) // chunk + 1) if window else (T - 1) // chunk + 1,
+                  chunk=chunk)
     return kernels.latent_attention(q_abs, q_rot, pool, table, P, positions, torch.zeros_like(positions), scale, **kw)
 
 
+# row sizes (r, rd): the second of each pair is one the tensor-core kernel takes in bfloat16
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("mode", ["rows", "tiles", "chunks"])
-def test_attention_kernel_sees_exactly_its_window(dtype, mode):
+@pytest.mark.parametrize("r,rd", [(24, 8), (32, 16)])
+def test_attention_kernel_sees_exactly_its_window(dtype, mode, r, rd):
     """One key per row is made to stand out: on the window's last position inside it owns the output, one
     position further it must not be seen at all.  Pages in a scrambled order; the window is no multiple of
     the key tile, the page or the chunk."""
     g = torch.Generator().manual_seed(5)
-    T, H, r, rd, P, window = 150, 4, 24, 8, 16, 37
+    T, H, P, window = 150, 4, 16, 37
     q = torch.randn(T, H, r + rd, generator=g).to(dtype)
     rows = (torch.randn(T, r + rd, generator=g) * 0.1).to(dtype)
     rows[:, :r] = torch.randn(T, r, generator=g).to(dtype) * 0.1 + torch.arange(T)[:, None] * 0.01
@@ -169,12 +172,13 @@ def test_attention_kernel_sees_exactly_its_window(dtype, mode):
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("mode", ["rows", "tiles", "chunks"])
-def test_attention_kernel_finds_a_far_key_and_counts_the_sink_once(dtype, mode):
+@pytest.mark.parametrize("r,rd", [(40, 4), (48, 16)])
+def test_attention_kernel_finds_a_far_key_and_counts_the_sink_once(dtype, mode, r, rd):
     """Causal rows over 300 keys in pages of 8.  Head 0 of the last row looks for the key at position 3 among
     hundreds; head 1's sink is so large that its output all but vanishes; head 2's so small that it does
     nothing; head 3 sits between (its share of the denominator is checked by the numbers)."""
     g = torch.Generator().manual_seed(8)
-    T, H, r, rd, P = 300, 4, 40, 4, 8
+    T, H, P = 300, 4, 8
     q = torch.randn(T, H, r + rd, generator=g).to(dtype)
     rows = (torch.randn(T, r + rd, generator=g) * 0.2).to(dtype)
     looks = q[T - 1, 0, r:].float()
@@ -195,6 +199,25 @@ def test_attention_kernel_finds_a_far_key_and_counts_the_sink_once(dtype, mode):
     s = float((rows[0].double() @ q[0, 3].double()) * 0.3)
     share = math.exp(s) / (math.exp(s) + math.exp(0.5))
     assert float((got[0, 3] - share * rows[0, :r].double()).abs().max()) < tol
+
+
+@pytest.mark.parametrize("mode", ["rows", "tiles", "chunks"])
+@pytest.mark.parametrize("H,r,rd,window,sinks", [(16, 512, 64, None, True), (40, 64, 32, 150, False),
+                                                 (6, 256, 16, 70, True), (3, 96, 48, None, False)])
+def test_attention_kernel_on_the_tensor_cores_at_other_sizes(mode, H, r, rd, window, sinks):
+    """bfloat16 rows of the widths and head counts a large model has (one and two tiles of 16 units, several
+    groups of heads, values that do not fill a warp's columns), against the plain attention on the same rounded
+    inputs."""
+    g = torch.Generator().manual_seed(H)
+    T, P = 210, 16
+    q = (torch.randn(T, H, r + rd, generator=g) * 0.5).to(torch.bfloat16)
+    rows = (torch.randn(T, r + rd, generator=g) * 0.3).to(torch.bfloat16)
+    sink = torch.randn(H, generator=g) * 2 if sinks else None
+    pool, table = paged(rows, P, torch.bfloat16, g)
+    scale = (r + rd) ** -0.5 * 2
+    got = run_kernel(q, pool, table, P, r, scale, window, sink, mode).float().cpu().double()
+    want = plain_shared_row_attention(q.double(), rows.double(), r, scale, window, None if sink is None else sink.double())
+    assert float((got - want).abs().max()) < 6e-3                       # one rounding of outputs below 1
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
