@@ -304,19 +304,17 @@ __global__ void latent_attention_kernel(
 }
 
 // ---------------------------------------------------------------------------------------------
-// bfloat16 on mma.sync (m16n8k16): a block of four warps serves 16 * MT (row, head) units over 64-key tiles
-// that come in by 16-byte cp.async, two stages.  Per tile: (1) S = Q K^T, each warp 16 of the tile's keys
-// over the whole row width (bfloat16 products are exact in float, float sums), scaled and left in shared
-// memory; (2) the softmax step in float, 128 / units threads per unit: mask, running maximum, weights and
-// their sum, the factor the sums so far shrink by; the float weights are split into two bfloat16 terms,
-// p = hi + lo with lo = bf16(p - hi), so that P keeps 16 mantissa bits; (3) O = O * factor + P V, each warp a
-// quarter of the value's columns (the value is the first r elements of the key row, read transposed by
-// ldmatrix) with both terms of P.  r and rd are multiples of 16.  A unit whose keys a tile does not touch
-// leaves the tile with its sums unchanged bit for bit, so a row's result does not depend on its neighbours.
-#define LM_KEYS 64
-#define LM_WARPS 4
-#define LM_S_STRIDE 68          // floats per row of S
-#define LM_P_STRIDE 144         // bytes per row of a P term: 64 keys of 2 bytes and 16 bytes of padding
+// bfloat16 on mma.sync (m16n8k16): a block of 4 * MTB warps serves 16 * MTB (row, head) units over tiles of KT
+// keys that come in by 16-byte cp.async, two stages.  The four warps of a group share one tile of 16 units.
+// Per key tile: (1) S = Q K^T, each warp a quarter of the tile's keys over the whole row width (bfloat16
+// products are exact in float, float sums), scaled and left in shared memory; (2) the softmax step in float,
+// eight threads per unit: mask, running maximum, weights and their sum, the factor the sums so far shrink
+// by; the float weights are split into two bfloat16 terms, p = hi + lo with lo = bf16(p - hi), so that P
+// keeps 16 mantissa bits; (3) O = O * factor + P V, each warp a quarter of the value's columns (the value is
+// the first r elements of the key row, read transposed by ldmatrix) with both terms of P.  r and rd are
+// multiples of 16.  A unit whose keys a tile does not touch leaves the tile with its sums unchanged bit for
+// bit, so a row's result does not depend on its neighbours.
+#define LM_S_PAD 4              // floats of padding per row of S
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -337,9 +335,16 @@ __device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* row)
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
 
-// MT: tiles of 16 units; NT: tiles of 8 value columns per warp (4 * 8 * NT >= r).
-template <int MT, int NT>
-__global__ void __launch_bounds__(LM_WARPS * 32, 1) latent_attention_mma_kernel(
+// Shared memory of a block, in bytes.
+static inline size_t lm_smem(int mtb, int kt, int k_stride) {
+  const size_t U = 16 * (size_t)mtb;
+  return 2 * (size_t)kt * k_stride + U * k_stride + U * (kt + LM_S_PAD) * 4 + 2 * U * (kt * 2 + 16) + 3 * U * 4;
+}
+
+// MTB: tiles of 16 units in the block; KT: keys per tile (32 or 64); NT: tiles of 8 value columns per warp
+// (4 * 8 * NT >= r).
+template <int MTB, int KT, int NT>
+__global__ void __launch_bounds__(128 * MTB, KT == 32 ? 2 : 1) latent_attention_mma_kernel(
     const bf16* __restrict__ q_abs, const bf16* __restrict__ q_rot, const bf16* __restrict__ pool,
     const int* __restrict__ block_table, int max_pages, int page_size, const int* __restrict__ positions,
     const int* __restrict__ row_seg, const int* __restrict__ tiles, bf16* __restrict__ out, int M, int H, int r,
@@ -347,10 +352,14 @@ __global__ void __launch_bounds__(LM_WARPS * 32, 1) latent_attention_mma_kernel(
     int num_chunks, float* __restrict__ part_o, float* __restrict__ part_ml) {
   pdl_begin();
   extern __shared__ __align__(16) unsigned char lm_raw[];
-  constexpr int U = 16 * MT;                             // unit rows of the block
-  constexpr int TPU = LM_WARPS * 32 / U;                 // threads per unit in the softmax step
-  constexpr int KPT = LM_KEYS / TPU;                     // keys per such thread
+  constexpr int U = 16 * MTB;                            // unit rows of the block
+  constexpr int THREADS = 128 * MTB;
+  constexpr int KPT = KT / 8;                            // keys per thread in the softmax step (8 threads a unit)
+  constexpr int KPW = KT / 4;                            // keys per warp in S = Q K^T
+  constexpr int S_STRIDE = KT + LM_S_PAD;                // floats per row of S
+  constexpr int P_STRIDE = KT * 2 + 16;                  // bytes per row of a P term
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int wm = warp >> 2, wq = warp & 3;               // this warp's tile of units, and its quarter
   const int m0 = tiles ? tiles[2 * blockIdx.x] : (int)blockIdx.x;
   const int rows = tiles ? tiles[2 * blockIdx.x + 1] : 1;
   const int h0 = blockIdx.y * hpb;
@@ -368,27 +377,30 @@ __global__ void __launch_bounds__(LM_WARPS * 32, 1) latent_attention_mma_kernel(
     lo = max(lo, cnk * chunk);
     hi = min(hi, (cnk + 1) * chunk - 1);
   }
-  const int stage_bytes = LM_KEYS * k_stride;
+  const int stage_bytes = KT * k_stride;
   unsigned char* qs = lm_raw + 2 * (size_t)stage_bytes;                  // [U][k_stride]
-  float* ss = reinterpret_cast<float*>(qs + (size_t)U * k_stride);        // [U][LM_S_STRIDE]
-  unsigned char* p_hi = reinterpret_cast<unsigned char*>(ss + U * LM_S_STRIDE);
-  unsigned char* p_lo = p_hi + U * LM_P_STRIDE;
-  float* m_s = reinterpret_cast<float*>(p_lo + U * LM_P_STRIDE);          // [U] running maximum
+  float* ss = reinterpret_cast<float*>(qs + (size_t)U * k_stride);        // [U][S_STRIDE]
+  unsigned char* p_hi = reinterpret_cast<unsigned char*>(ss + U * S_STRIDE);
+  unsigned char* p_lo = p_hi + U * P_STRIDE;
+  float* m_s = reinterpret_cast<float*>(p_lo + U * P_STRIDE);             // [U] running maximum
   float* l_s = m_s + U;                                                   // [U] running sum
   float* c_s = l_s + U;                                                   // [U] this tile's factor
 
   // the units' queries: [absorbed r, rotated rd] per row, zeros for rows beyond the block's units
   const int per = kw / 8;
-  for (int i = tid; i < U * per; i += LM_WARPS * 32) {
-    const int u = i / per, d = (i - u * per) * 8;
-    uint4 v = make_uint4(0, 0, 0, 0);
+  for (int u = warp; u < U; u += 4 * MTB) {
+    const bf16* a_src = nullptr;
+    const bf16* r_src = nullptr;
     if (u < units) {
       const int rr = u / nh, h = h0 + (u - rr * nh);
-      const bf16* src = d < r ? q_abs + ((size_t)h * M + m0 + rr) * r + d
-                              : q_rot + ((size_t)(m0 + rr) * H + h) * rd + (d - r);
-      v = *reinterpret_cast<const uint4*>(src);
+      a_src = q_abs + ((size_t)h * M + m0 + rr) * r;
+      r_src = q_rot + ((size_t)(m0 + rr) * H + h) * rd - r;
     }
-    *reinterpret_cast<uint4*>(qs + (size_t)u * k_stride + d * 2) = v;
+    for (int c = lane; c < per; c += 32) {
+      uint4 v = make_uint4(0, 0, 0, 0);
+      if (a_src) v = *reinterpret_cast<const uint4*>((c * 8 < r ? a_src : r_src) + c * 8);
+      *reinterpret_cast<uint4*>(qs + (size_t)u * k_stride + c * 16) = v;
+    }
   }
   if (tid < U) {
     const bool with_sink = sink && first_chunk && tid < units;
@@ -396,82 +408,94 @@ __global__ void __launch_bounds__(LM_WARPS * 32, 1) latent_attention_mma_kernel(
     l_s[tid] = with_sink ? 1.f : 0.f;
   }
   const int* bt = block_table + (size_t)row_seg[m0] * max_pages;
-  const int t_first = (lo / LM_KEYS) * LM_KEYS;
-  const int ntiles = (hi - t_first) / LM_KEYS + 1;
+  const int t_first = (lo / KT) * KT;
+  const int ntiles = (hi - t_first) / KT + 1;
 
+  // a warp brings whole key rows in: one page lookup per row, the lanes its 16-byte pieces
   auto issue = [&](int tile) {
     if (tile < ntiles) {
-      const int t0 = t_first + tile * LM_KEYS;
+      const int t0 = t_first + tile * KT;
       unsigned char* ks = lm_raw + (size_t)(tile & 1) * stage_bytes;
-      for (int v = tid; v < LM_KEYS * per; v += LM_WARPS * 32) {
-        const int j = v / per, c = v - j * per;
+      for (int j = warp; j < KT; j += 4 * MTB) {
         const int kp = t0 + j;
         const bool valid = kp >= lo && kp <= hi;
         const bf16* src = pool;
-        if (valid) src = pool + ((size_t)bt[kp / page_size] * page_size + kp % page_size) * kw + c * 8;
-        la_cp_async16(ks + j * k_stride + c * 16, src, valid);
+        if (valid) src = pool + ((size_t)bt[kp / page_size] * page_size + kp % page_size) * kw;
+        unsigned char* dst = ks + (size_t)j * k_stride;
+        for (int c = lane; c < per; c += 32) la_cp_async16(dst + c * 16, valid ? src + c * 8 : src, valid);
       }
     }
     la_cp_async_commit();
   };
 
-  float oacc[MT][NT][4];
+  float oacc[NT][4];
 #pragma unroll
-  for (int mt = 0; mt < MT; ++mt)
+  for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) oacc[mt][nt][e] = 0.f;
+    for (int e = 0; e < 4; ++e) oacc[nt][e] = 0.f;
 
-  // the softmax step's unit of this thread
-  const int su = tid / TPU, sub = tid % TPU;
+  // the softmax step's unit of this thread: eight threads side by side per unit
+  const int su = tid >> 3, sub = tid & 7;
   const int s_p = pos0 + (su < units ? su / nh : 0);
-  const int col_w = warp * 8 * NT;                        // this warp's first value column
+  const int col_w = wq * 8 * NT;                          // this warp's first value column
 
   issue(0);
   for (int tile = 0; tile < ntiles; ++tile) {
     la_cp_async_wait<0>();
     __syncthreads();                                     // the tile is in; the step before is over everywhere
     issue(tile + 1);
-    const int t0 = t_first + tile * LM_KEYS;
+    const int t0 = t_first + tile * KT;
     const unsigned char* ks = lm_raw + (size_t)(tile & 1) * stage_bytes;
 
-    // (1) S = Q K^T for this warp's 16 keys
+    // (1) S = Q K^T for this warp's units and its KPW keys
     {
-      float sacc[MT][2][4];
+      float sacc[KPW / 8][4];
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt)
+      for (int n = 0; n < KPW / 8; ++n)
 #pragma unroll
-        for (int n = 0; n < 2; ++n)
-#pragma unroll
-          for (int e = 0; e < 4; ++e) sacc[mt][n][e] = 0.f;
-      const unsigned char* k_at = ks + (size_t)(warp * 16 + (lane >> 4) * 8 + (lane & 7)) * k_stride + ((lane >> 3) & 1) * 16;
-      const unsigned char* q_at = qs + (size_t)(lane & 15) * k_stride + (lane >> 4) * 16;
-      for (int kk = 0; kk < kw / 16; ++kk) {
-        uint32_t bk[4];
-        ldsm_x4(bk, k_at + kk * 32);
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-          uint32_t a[4];
-          ldsm_x4(a, q_at + (size_t)mt * 16 * k_stride + kk * 32);
-          mma_bf16_16816(sacc[mt][0], a, bk[0], bk[1]);
-          mma_bf16_16816(sacc[mt][1], a, bk[2], bk[3]);
+        for (int e = 0; e < 4; ++e) sacc[n][e] = 0.f;
+      const unsigned char* q_at = qs + (size_t)(wm * 16 + (lane & 15)) * k_stride + (lane >> 4) * 16;
+      if (KPW == 16) {
+        // 16 keys: one load holds the fragments of two tiles of 8 keys for one step of 16 dimensions
+        const unsigned char* k_at = ks + (size_t)(wq * 16 + (lane >> 4) * 8 + (lane & 7)) * k_stride + ((lane >> 3) & 1) * 16;
+        for (int kk = 0; kk < kw / 16; ++kk) {
+          uint32_t bk[4], a[4];
+          ldsm_x4(bk, k_at + kk * 32);
+          ldsm_x4(a, q_at + kk * 32);
+          mma_bf16_16816(sacc[0], a, bk[0], bk[1]);
+          mma_bf16_16816(sacc[KPW / 8 - 1], a, bk[2], bk[3]);
+        }
+      } else {
+        // 8 keys: one load holds the fragments for two steps of 16 dimensions
+        const unsigned char* k_at = ks + (size_t)(wq * 8 + (lane & 7)) * k_stride + (lane >> 3) * 16;
+        int kk = 0;
+        for (; kk + 1 < kw / 16; kk += 2) {
+          uint32_t bk[4], a[4];
+          ldsm_x4(bk, k_at + kk * 32);
+          ldsm_x4(a, q_at + kk * 32);
+          mma_bf16_16816(sacc[0], a, bk[0], bk[1]);
+          ldsm_x4(a, q_at + kk * 32 + 32);
+          mma_bf16_16816(sacc[0], a, bk[2], bk[3]);
+        }
+        if (kk < kw / 16) {                               // an odd number of steps: the last load's second half
+          uint32_t bk[4], a[4];                           // repeats the step before and is not used
+          ldsm_x4(bk, k_at + kk * 32 - ((lane >> 4) ? 32 : 0));
+          ldsm_x4(a, q_at + kk * 32);
+          mma_bf16_16816(sacc[0], a, bk[0], bk[1]);
         }
       }
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int n = 0; n < 2; ++n) {
-          float* at = ss + (mt * 16 + (lane >> 2)) * LM_S_STRIDE + warp * 16 + n * 8 + (lane & 3) * 2;
-          at[0] = sacc[mt][n][0] * scale;
-          at[1] = sacc[mt][n][1] * scale;
-          at[8 * LM_S_STRIDE] = sacc[mt][n][2] * scale;
-          at[8 * LM_S_STRIDE + 1] = sacc[mt][n][3] * scale;
-        }
+      for (int n = 0; n < KPW / 8; ++n) {
+        float* at = ss + (wm * 16 + (lane >> 2)) * S_STRIDE + wq * KPW + n * 8 + (lane & 3) * 2;
+        at[0] = sacc[n][0] * scale;
+        at[1] = sacc[n][1] * scale;
+        at[8 * S_STRIDE] = sacc[n][2] * scale;
+        at[8 * S_STRIDE + 1] = sacc[n][3] * scale;
+      }
     }
     __syncthreads();
 
-    // (2) the softmax step of unit su, TPU threads side by side
+    // (2) the softmax step of unit su
     {
       const int klo = max(lo, window > 0 ? s_p - window + 1 : 0);
       const int khi = su < units ? min(s_p, hi) : -1;
@@ -481,17 +505,17 @@ __global__ void __launch_bounds__(LM_WARPS * 32, 1) latent_attention_mma_kernel(
       for (int j = 0; j < KPT; ++j) {
         const int kp = t0 + sub * KPT + j;
         const bool valid = kp >= klo && kp <= khi;
-        sv[j] = valid ? ss[su * LM_S_STRIDE + sub * KPT + j] : -INFINITY;
+        sv[j] = valid ? ss[su * S_STRIDE + sub * KPT + j] : -INFINITY;
         mx = fmaxf(mx, sv[j]);
       }
 #pragma unroll
-      for (int o = TPU / 2; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+      for (int o = 4; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
       const float m_old = m_s[su];
       const float m_new = fmaxf(m_old, mx);
       const float corr = m_new == -INFINITY ? 1.f : expf(m_old - m_new);
       float sum = 0.f;
-      __nv_bfloat16* ph = reinterpret_cast<__nv_bfloat16*>(p_hi + su * LM_P_STRIDE) + sub * KPT;
-      __nv_bfloat16* pl = reinterpret_cast<__nv_bfloat16*>(p_lo + su * LM_P_STRIDE) + sub * KPT;
+      __nv_bfloat16* ph = reinterpret_cast<__nv_bfloat16*>(p_hi + su * P_STRIDE) + sub * KPT;
+      __nv_bfloat16* pl = reinterpret_cast<__nv_bfloat16*>(p_lo + su * P_STRIDE) + sub * KPT;
 #pragma unroll
       for (int j = 0; j < KPT; ++j) {
         const float pw = sv[j] == -INFINITY ? 0.f : expf(sv[j] - m_new);
@@ -501,7 +525,7 @@ __global__ void __launch_bounds__(LM_WARPS * 32, 1) latent_attention_mma_kernel(
         pl[j] = __float2bfloat16_rn(pw - __bfloat162float(hi16));
       }
 #pragma unroll
-      for (int o = TPU / 2; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+      for (int o = 4; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
       __syncwarp();
       if (sub == 0) {
         m_s[su] = m_new;
@@ -511,41 +535,32 @@ __global__ void __launch_bounds__(LM_WARPS * 32, 1) latent_attention_mma_kernel(
     }
     __syncthreads();
 
-    // (3) O = O * factor + P V for this warp's columns
+    // (3) O = O * factor + P V for this warp's units and columns
     {
+      const float c_lo = c_s[wm * 16 + (lane >> 2)], c_hi = c_s[wm * 16 + (lane >> 2) + 8];
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
-        const float c_lo = c_s[mt * 16 + (lane >> 2)], c_hi = c_s[mt * 16 + (lane >> 2) + 8];
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          oacc[mt][nt][0] *= c_lo;
-          oacc[mt][nt][1] *= c_lo;
-          oacc[mt][nt][2] *= c_hi;
-          oacc[mt][nt][3] *= c_hi;
-        }
+      for (int nt = 0; nt < NT; ++nt) {
+        oacc[nt][0] *= c_lo;
+        oacc[nt][1] *= c_lo;
+        oacc[nt][2] *= c_hi;
+        oacc[nt][3] *= c_hi;
       }
       const unsigned char* v_at = ks + (size_t)(((lane >> 3) & 1) * 8 + (lane & 7)) * k_stride + (col_w + (lane >> 4) * 8) * 2;
+      const size_t p_at = (size_t)(wm * 16 + (lane & 15)) * P_STRIDE + (lane >> 4) * 16;
 #pragma unroll
-      for (int kk = 0; kk < LM_KEYS / 16; ++kk) {
-        uint32_t a_hi[MT][4], a_lo[MT][4];
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-          const size_t at = (size_t)(mt * 16 + (lane & 15)) * LM_P_STRIDE + kk * 32 + (lane >> 4) * 16;
-          ldsm_x4(a_hi[mt], p_hi + at);
-          ldsm_x4(a_lo[mt], p_lo + at);
-        }
+      for (int kk = 0; kk < KT / 16; ++kk) {
+        uint32_t a_hi[4], a_lo[4];
+        ldsm_x4(a_hi, p_hi + p_at + kk * 32);
+        ldsm_x4(a_lo, p_lo + p_at + kk * 32);
 #pragma unroll
         for (int np = 0; np < NT / 2; ++np) {
           if (col_w + np * 16 >= r) break;                // columns beyond the value (the same for the whole warp)
           uint32_t bv[4];
           ldsm_x4_trans(bv, v_at + (size_t)kk * 16 * k_stride + np * 32);
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt) {
-            mma_bf16_16816(oacc[mt][2 * np], a_hi[mt], bv[0], bv[1]);
-            mma_bf16_16816(oacc[mt][2 * np], a_lo[mt], bv[0], bv[1]);
-            mma_bf16_16816(oacc[mt][2 * np + 1], a_hi[mt], bv[2], bv[3]);
-            mma_bf16_16816(oacc[mt][2 * np + 1], a_lo[mt], bv[2], bv[3]);
-          }
+          mma_bf16_16816(oacc[2 * np], a_hi, bv[0], bv[1]);
+          mma_bf16_16816(oacc[2 * np + 1], a_hi, bv[2], bv[3]);
+          mma_bf16_16816(oacc[2 * np], a_lo, bv[0], bv[1]);
+          mma_bf16_16816(oacc[2 * np + 1], a_lo, bv[2], bv[3]);
         }
       }
     }
@@ -554,38 +569,36 @@ __global__ void __launch_bounds__(LM_WARPS * 32, 1) latent_attention_mma_kernel(
   __syncthreads();
 
 #pragma unroll
-  for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-      const int u = mt * 16 + (lane >> 2) + half * 8;
-      if (u >= units) continue;
-      const int rr = u / nh, h = h0 + (u - rr * nh);
-      if (num_chunks > 1) {
-        const size_t slot = ((size_t)blockIdx.x * H + h) * num_chunks + blockIdx.z;
-#pragma unroll
-        for (int nt = 0; nt < NT; ++nt) {
-          const int col = col_w + nt * 8 + (lane & 3) * 2;
-          if (col < r) {
-            part_o[slot * r + col] = oacc[mt][nt][half * 2];
-            part_o[slot * r + col + 1] = oacc[mt][nt][half * 2 + 1];
-          }
-        }
-        if (warp == 0 && (lane & 3) == 0) {
-          part_ml[slot * 2] = m_s[u];
-          part_ml[slot * 2 + 1] = l_s[u];
-        }
-        continue;
-      }
-      const float inv = 1.f / l_s[u];
-      bf16* dst = out + ((size_t)(m0 + rr) * H + h) * r;
+  for (int half = 0; half < 2; ++half) {
+    const int u = wm * 16 + (lane >> 2) + half * 8;
+    if (u >= units) continue;
+    const int rr = u / nh, h = h0 + (u - rr * nh);
+    if (num_chunks > 1) {
+      const size_t slot = ((size_t)blockIdx.x * H + h) * num_chunks + blockIdx.z;
 #pragma unroll
       for (int nt = 0; nt < NT; ++nt) {
         const int col = col_w + nt * 8 + (lane & 3) * 2;
-        if (col < r)
-          *reinterpret_cast<__nv_bfloat162*>(dst + col) =
-              __floats2bfloat162_rn(oacc[mt][nt][half * 2] * inv, oacc[mt][nt][half * 2 + 1] * inv);
+        if (col < r) {
+          part_o[slot * r + col] = oacc[nt][half * 2];
+          part_o[slot * r + col + 1] = oacc[nt][half * 2 + 1];
+        }
       }
+      if (wq == 0 && (lane & 3) == 0) {
+        part_ml[slot * 2] = m_s[u];
+        part_ml[slot * 2 + 1] = l_s[u];
+      }
+      continue;
     }
+    const float inv = 1.f / l_s[u];
+    bf16* dst = out + ((size_t)(m0 + rr) * H + h) * r;
+#pragma unroll
+    for (int nt = 0; nt < NT; ++nt) {
+      const int col = col_w + nt * 8 + (lane & 3) * 2;
+      if (col < r)
+        *reinterpret_cast<__nv_bfloat162*>(dst + col) =
+            __floats2bfloat162_rn(oacc[nt][half * 2] * inv, oacc[nt][half * 2 + 1] * inv);
+    }
+  }
 }
 
 // Whether the tensor-core kernel takes these sizes (bfloat16 only).  SNOWLLM_B200_LATENT_MMA=0 in the
@@ -618,42 +631,52 @@ SNK_API int snk_latent_attention(const void* q_abs, const void* q_rot, const voi
   if (num_chunks > 1 && (tiles != nullptr || scratch == nullptr)) return SNK_ERR_SIZE;
   if (lm_ok(r, rd, dtype) && ((uintptr_t)pool % 16) == 0 && ((uintptr_t)q_abs % 16) == 0 &&
       ((uintptr_t)q_rot % 16) == 0) {
-    if (chunk % LM_KEYS) return SNK_ERR_SIZE;
+    if (chunk % 64) return SNK_ERR_SIZE;
     const int hpb = lm_heads_per_block(H);
     if (tile_rows < 1 || (tiles && tile_rows * hpb > 32)) return SNK_ERR_SIZE;
     const int units_max = (tiles ? tile_rows : 1) * hpb;
-    const int mt = units_max > 16 ? 2 : 1;
+    const int mtb = units_max > 16 ? 2 : 1;
     const int groups = (H + hpb - 1) / hpb;
     if (groups > 65535) return SNK_ERR_SIZE;
     const int kw = r + rd;
-    int k_stride = kw * 2 + 16;                          // a multiple of 32 bytes and 16: an odd number of 16-byte units
-    const int U = 16 * mt;
-    const size_t smem = 2 * (size_t)LM_KEYS * k_stride + (size_t)U * k_stride + (size_t)U * LM_S_STRIDE * 4 +
-                        2 * (size_t)U * LM_P_STRIDE + 3 * (size_t)U * 4;
+    const int k_stride = kw * 2 + 16;                    // kw * 2 is a multiple of 32: an odd number of 16-byte units
+    // keys per tile: 32 where two blocks then fit an SM (rows alone, whose blocks wait for memory most of the
+    // time), else 64; SNOWLLM_B200_LATENT_KEYS=32|64 fixes it (A/B runs)
+    static int keys_env = -1;
+    if (keys_env < 0) {
+      const char* e = getenv("SNOWLLM_B200_LATENT_KEYS");
+      keys_env = e ? atoi(e) : 0;
+    }
+    int kt = (!tiles && lm_smem(mtb, 32, k_stride) <= 113 * 1024) ? 32 : 64;
+    if (keys_env == 32 || keys_env == 64) kt = keys_env;
+    if (lm_smem(mtb, kt, k_stride) > 227 * 1024) kt = 32;
+    const size_t smem = lm_smem(mtb, kt, k_stride);
     if (smem > 227 * 1024) return SNK_ERR_SIZE;
     float* part_o = static_cast<float*>(scratch);
     float* part_ml = part_o ? part_o + (size_t)M * H * num_chunks * r : nullptr;
     dim3 grid(n_tiles, groups, num_chunks);
-#define LM_LAUNCH(MT_, NT_)                                                                                     \
+#define LM_LAUNCH(MTB_, KT_, NT_)                                                                               \
   do {                                                                                                          \
     if (smem > 48 * 1024)                                                                                       \
-      cudaFuncSetAttribute(latent_attention_mma_kernel<MT_, NT_>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
-                           (int)smem);                                                                          \
-    snk_launch(latent_attention_mma_kernel<MT_, NT_>, dim3(grid), dim3(LM_WARPS * 32), smem, stream,            \
+      cudaFuncSetAttribute(latent_attention_mma_kernel<MTB_, KT_, NT_>,                                         \
+                           cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                             \
+    snk_launch(latent_attention_mma_kernel<MTB_, KT_, NT_>, dim3(grid), dim3(128 * MTB_), smem, stream,         \
                static_cast<const bf16*>(q_abs), static_cast<const bf16*>(q_rot), static_cast<const bf16*>(pool),\
                block_table, max_pages, page_size, positions, row_seg, tiles, static_cast<bf16*>(out), M, H, r,  \
                rd, hpb, window, scale, sink, k_stride, chunk, num_chunks, part_o, part_ml);                     \
   } while (0)
-#define LM_PICK(MT_)                                   \
+#define LM_PICK_NT(MTB_, KT_)                          \
   do {                                                 \
-    if (r <= 64) LM_LAUNCH(MT_, 2);                    \
-    else if (r <= 128) LM_LAUNCH(MT_, 4);              \
-    else if (r <= 256) LM_LAUNCH(MT_, 8);              \
-    else LM_LAUNCH(MT_, 16);                           \
+    if (r <= 64) LM_LAUNCH(MTB_, KT_, 2);              \
+    else if (r <= 128) LM_LAUNCH(MTB_, KT_, 4);        \
+    else if (r <= 256) LM_LAUNCH(MTB_, KT_, 8);        \
+    else LM_LAUNCH(MTB_, KT_, 16);                     \
   } while (0)
-    if (mt == 2) LM_PICK(2);
-    else LM_PICK(1);
-#undef LM_PICK
+    if (mtb == 2 && kt == 64) LM_PICK_NT(2, 64);
+    else if (mtb == 2) LM_PICK_NT(2, 32);
+    else if (kt == 64) LM_PICK_NT(1, 64);
+    else LM_PICK_NT(1, 32);
+#undef LM_PICK_NT
 #undef LM_LAUNCH
     SNK_LAUNCH_CHECK();
     return 0;
