@@ -304,7 +304,7 @@ __global__ void latent_attention_kernel(
 }
 
 // ---------------------------------------------------------------------------------------------
-// bfloat16 on mma.sync (m16n8k16): a block of 4 * MTB warps serves 16 * MTB (row, head) units over tiles of KT
+// bfloat16 on mma.sync (m16n8k16): a block of 4 * MTB warps (MTB 1, 2 or 4) serves 16 * MTB (row, head) units over tiles of KT
 // keys that come in by 16-byte cp.async, two stages.  The four warps of a group share one tile of 16 units.
 // Per key tile: (1) S = Q K^T, each warp a quarter of the tile's keys over the whole row width (bfloat16
 // products are exact in float, float sums), scaled and left in shared memory; (2) the softmax step in float,
@@ -344,7 +344,7 @@ static inline size_t lm_smem(int mtb, int kt, int k_stride) {
 // MTB: tiles of 16 units in the block; KT: keys per tile (32 or 64); NT: tiles of 8 value columns per warp
 // (4 * 8 * NT >= r).
 template <int MTB, int KT, int NT>
-__global__ void __launch_bounds__(128 * MTB, KT == 32 ? 2 : 1) latent_attention_mma_kernel(
+__global__ void __launch_bounds__(128 * MTB, (KT == 32 && MTB == 1) ? 2 : 1) latent_attention_mma_kernel(
     const bf16* __restrict__ q_abs, const bf16* __restrict__ q_rot, const bf16* __restrict__ pool,
     const int* __restrict__ block_table, int max_pages, int page_size, const int* __restrict__ positions,
     const int* __restrict__ row_seg, const int* __restrict__ tiles, bf16* __restrict__ out, int M, int H, int r,
@@ -449,16 +449,31 @@ __global__ void __launch_bounds__(128 * MTB, KT == 32 ? 2 : 1) latent_attention_
 
     // (1) S = Q K^T for this warp's units and its KPW keys
     {
-      float sacc[KPW / 8][4];
+      // two sets of accumulators, for even and odd steps of 16 dimensions: an MMA then waits for the one four
+      // (two) instructions back, not for the one right before it
+      float sacc[KPW / 8][4], sodd[KPW / 8][4];
 #pragma unroll
       for (int n = 0; n < KPW / 8; ++n)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) sacc[n][e] = 0.f;
+        for (int e = 0; e < 4; ++e) sacc[n][e] = sodd[n][e] = 0.f;
       const unsigned char* q_at = qs + (size_t)(wm * 16 + (lane & 15)) * k_stride + (lane >> 4) * 16;
+      const int steps = kw / 16;
       if (KPW == 16) {
         // 16 keys: one load holds the fragments of two tiles of 8 keys for one step of 16 dimensions
         const unsigned char* k_at = ks + (size_t)(wq * 16 + (lane >> 4) * 8 + (lane & 7)) * k_stride + ((lane >> 3) & 1) * 16;
-        for (int kk = 0; kk < kw / 16; ++kk) {
+        int kk = 0;
+        for (; kk + 1 < steps; kk += 2) {
+          uint32_t bk[4], a[4], bk2[4], a2[4];
+          ldsm_x4(bk, k_at + kk * 32);
+          ldsm_x4(a, q_at + kk * 32);
+          ldsm_x4(bk2, k_at + kk * 32 + 32);
+          ldsm_x4(a2, q_at + kk * 32 + 32);
+          mma_bf16_16816(sacc[0], a, bk[0], bk[1]);
+          mma_bf16_16816(sacc[KPW / 8 - 1], a, bk[2], bk[3]);
+          mma_bf16_16816(sodd[0], a2, bk2[0], bk2[1]);
+          mma_bf16_16816(sodd[KPW / 8 - 1], a2, bk2[2], bk2[3]);
+        }
+        if (kk < steps) {
           uint32_t bk[4], a[4];
           ldsm_x4(bk, k_at + kk * 32);
           ldsm_x4(a, q_at + kk * 32);
@@ -469,21 +484,25 @@ __global__ void __launch_bounds__(128 * MTB, KT == 32 ? 2 : 1) latent_attention_
         // 8 keys: one load holds the fragments for two steps of 16 dimensions
         const unsigned char* k_at = ks + (size_t)(wq * 8 + (lane & 7)) * k_stride + (lane >> 3) * 16;
         int kk = 0;
-        for (; kk + 1 < kw / 16; kk += 2) {
-          uint32_t bk[4], a[4];
+        for (; kk + 1 < steps; kk += 2) {
+          uint32_t bk[4], a[4], a2[4];
           ldsm_x4(bk, k_at + kk * 32);
           ldsm_x4(a, q_at + kk * 32);
+          ldsm_x4(a2, q_at + kk * 32 + 32);
           mma_bf16_16816(sacc[0], a, bk[0], bk[1]);
-          ldsm_x4(a, q_at + kk * 32 + 32);
-          mma_bf16_16816(sacc[0], a, bk[2], bk[3]);
+          mma_bf16_16816(sodd[0], a2, bk[2], bk[3]);
         }
-        if (kk < kw / 16) {                               // an odd number of steps: the last load's second half
+        if (kk < steps) {                                 // an odd number of steps: the last load's second half
           uint32_t bk[4], a[4];                           // repeats the step before and is not used
           ldsm_x4(bk, k_at + kk * 32 - ((lane >> 4) ? 32 : 0));
           ldsm_x4(a, q_at + kk * 32);
           mma_bf16_16816(sacc[0], a, bk[0], bk[1]);
         }
       }
+#pragma unroll
+      for (int n = 0; n < KPW / 8; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sacc[n][e] += sodd[n][e];
 #pragma unroll
       for (int n = 0; n < KPW / 8; ++n) {
         float* at = ss + (wm * 16 + (lane >> 2)) * S_STRIDE + wq * KPW + n * 8 + (lane & 3) * 2;
@@ -552,15 +571,26 @@ __global__ void __launch_bounds__(128 * MTB, KT == 32 ? 2 : 1) latent_attention_
         uint32_t a_hi[4], a_lo[4];
         ldsm_x4(a_hi, p_hi + p_at + kk * 32);
         ldsm_x4(a_lo, p_lo + p_at + kk * 32);
+        // 32 columns at a time: eight independent MMAs between an accumulator's two terms
 #pragma unroll
-        for (int np = 0; np < NT / 2; ++np) {
+        for (int np = 0; np < NT / 2; np += 2) {
           if (col_w + np * 16 >= r) break;                // columns beyond the value (the same for the whole warp)
-          uint32_t bv[4];
+          uint32_t bv[4], bw[4];
           ldsm_x4_trans(bv, v_at + (size_t)kk * 16 * k_stride + np * 32);
+          const bool two = NT >= 4 && col_w + np * 16 + 16 < r;
+          if (two) ldsm_x4_trans(bw, v_at + (size_t)kk * 16 * k_stride + np * 32 + 32);
           mma_bf16_16816(oacc[2 * np], a_hi, bv[0], bv[1]);
           mma_bf16_16816(oacc[2 * np + 1], a_hi, bv[2], bv[3]);
+          if (two) {
+            mma_bf16_16816(oacc[(2 * np + 2) % NT], a_hi, bw[0], bw[1]);
+            mma_bf16_16816(oacc[(2 * np + 3) % NT], a_hi, bw[2], bw[3]);
+          }
           mma_bf16_16816(oacc[2 * np], a_lo, bv[0], bv[1]);
           mma_bf16_16816(oacc[2 * np + 1], a_lo, bv[2], bv[3]);
+          if (two) {
+            mma_bf16_16816(oacc[(2 * np + 2) % NT], a_lo, bw[0], bw[1]);
+            mma_bf16_16816(oacc[(2 * np + 3) % NT], a_lo, bw[2], bw[3]);
+          }
         }
       }
     }
@@ -611,12 +641,13 @@ static inline bool lm_ok(int r, int rd, int dtype) {
   }
   return on && dtype == SNK_BF16 && r % 16 == 0 && rd % 16 == 0 && r >= 16 && r <= 512;
 }
+#define LM_MAX_UNITS 64          // units of a block of 16 warps: four tiles of 16
 static inline int lm_heads_per_block(int H) { return H < 32 ? H : 32; }
 
 // Heads a block takes, and the rows of one request it serves beside each other, for H heads.
 static inline int la_heads_per_block(int H) { return H < LA_UPW * LA_MAX_WARPS ? H : LA_UPW * LA_MAX_WARPS; }
 SNK_API int snk_latent_attention_tile_rows(int H, int r, int rd, int dtype) {
-  const int rows = lm_ok(r, rd, dtype) ? 32 / lm_heads_per_block(H) : (LA_UPW * LA_MAX_WARPS) / la_heads_per_block(H);
+  const int rows = lm_ok(r, rd, dtype) ? LM_MAX_UNITS / lm_heads_per_block(H) : (LA_UPW * LA_MAX_WARPS) / la_heads_per_block(H);
   return rows < 1 ? 1 : rows;
 }
 
@@ -633,9 +664,9 @@ SNK_API int snk_latent_attention(const void* q_abs, const void* q_rot, const voi
       ((uintptr_t)q_rot % 16) == 0) {
     if (chunk % 64) return SNK_ERR_SIZE;
     const int hpb = lm_heads_per_block(H);
-    if (tile_rows < 1 || (tiles && tile_rows * hpb > 32)) return SNK_ERR_SIZE;
+    if (tile_rows < 1 || (tiles && tile_rows * hpb > LM_MAX_UNITS)) return SNK_ERR_SIZE;
     const int units_max = (tiles ? tile_rows : 1) * hpb;
-    const int mtb = units_max > 16 ? 2 : 1;
+    const int mtb = units_max > 32 ? 4 : (units_max > 16 ? 2 : 1);
     const int groups = (H + hpb - 1) / hpb;
     if (groups > 65535) return SNK_ERR_SIZE;
     const int kw = r + rd;
@@ -649,7 +680,7 @@ SNK_API int snk_latent_attention(const void* q_abs, const void* q_rot, const voi
     }
     int kt = (!tiles && lm_smem(mtb, 32, k_stride) <= 113 * 1024) ? 32 : 64;
     if (keys_env == 32 || keys_env == 64) kt = keys_env;
-    if (lm_smem(mtb, kt, k_stride) > 227 * 1024) kt = 32;
+    if (mtb == 4 || lm_smem(mtb, kt, k_stride) > 227 * 1024) kt = 32;      // sixteen warps: 32-key tiles only
     const size_t smem = lm_smem(mtb, kt, k_stride);
     if (smem > 227 * 1024) return SNK_ERR_SIZE;
     float* part_o = static_cast<float*>(scratch);
@@ -672,7 +703,8 @@ SNK_API int snk_latent_attention(const void* q_abs, const void* q_rot, const voi
     else if (r <= 256) LM_LAUNCH(MTB_, KT_, 8);        \
     else LM_LAUNCH(MTB_, KT_, 16);                     \
   } while (0)
-    if (mtb == 2 && kt == 64) LM_PICK_NT(2, 64);
+    if (mtb == 4) LM_PICK_NT(4, 32);
+    else if (mtb == 2 && kt == 64) LM_PICK_NT(2, 64);
     else if (mtb == 2) LM_PICK_NT(2, 32);
     else if (kt == 64) LM_PICK_NT(1, 64);
     else LM_PICK_NT(1, 32);

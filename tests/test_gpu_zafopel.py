@@ -205,7 +205,7 @@ def test_attention_kernel_finds_a_far_key_and_counts_the_sink_once(dtype, mode, 
 @pytest.mark.parametrize("H,r,rd,window,sinks", [(16, 512, 64, None, True), (40, 64, 32, 150, False),
                                                  (6, 256, 16, 70, True), (3, 96, 48, None, False)])
 def test_attention_kernel_on_the_tensor_cores_at_other_sizes(mode, H, r, rd, window, sinks):
-    """bfloat16 rows of the widths and head counts a large model has (one and two tiles of 16 units, several
+    """bfloat16 rows of the widths and head counts a large model has (one, two and four tiles of 16 units, several
     groups of heads, values that do not fill a warp's columns), against the plain attention on the same rounded
     inputs."""
     g = torch.Generator().manual_seed(H)
