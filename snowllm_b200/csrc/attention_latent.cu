@@ -335,6 +335,13 @@ __device__ __forceinline__ void ldsm_x4_trans(uint32_t (&r)[4], const void* row)
                : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
 }
 
+// e^x as 2^(x log2 e) on the special-function unit (two units in the last place; e^-inf = 0)
+__device__ __forceinline__ float lm_exp(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x * 1.4426950408889634f));
+  return y;
+}
+
 // Shared memory of a block, in bytes.
 static inline size_t lm_smem(int mtb, int kt, int k_stride) {
   const size_t U = 16 * (size_t)mtb;
@@ -531,13 +538,14 @@ __global__ void __launch_bounds__(128 * MTB, (KT == 32 && MTB == 1) ? 2 : 1) lat
       for (int o = 4; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
       const float m_old = m_s[su];
       const float m_new = fmaxf(m_old, mx);
-      const float corr = m_new == -INFINITY ? 1.f : expf(m_old - m_new);
+      const float m_ref = m_new == -INFINITY ? 0.f : m_new;       // nothing seen yet: every term below is e^-inf = 0
+      const float corr = lm_exp(m_old - m_ref);                   // e^0 = 1 exactly for a unit the tile does not touch
       float sum = 0.f;
       __nv_bfloat16* ph = reinterpret_cast<__nv_bfloat16*>(p_hi + su * P_STRIDE) + sub * KPT;
       __nv_bfloat16* pl = reinterpret_cast<__nv_bfloat16*>(p_lo + su * P_STRIDE) + sub * KPT;
 #pragma unroll
       for (int j = 0; j < KPT; ++j) {
-        const float pw = sv[j] == -INFINITY ? 0.f : expf(sv[j] - m_new);
+        const float pw = lm_exp(sv[j] - m_ref);
         sum += pw;
         const __nv_bfloat16 hi16 = __float2bfloat16_rn(pw);
         ph[j] = hi16;
@@ -557,12 +565,14 @@ __global__ void __launch_bounds__(128 * MTB, (KT == 32 && MTB == 1) ? 2 : 1) lat
     // (3) O = O * factor + P V for this warp's units and columns
     {
       const float c_lo = c_s[wm * 16 + (lane >> 2)], c_hi = c_s[wm * 16 + (lane >> 2) + 8];
+      if (!__all_sync(0xffffffffu, c_lo == 1.f && c_hi == 1.f)) {       // no maximum of the warp's units has grown
 #pragma unroll
-      for (int nt = 0; nt < NT; ++nt) {
-        oacc[nt][0] *= c_lo;
-        oacc[nt][1] *= c_lo;
-        oacc[nt][2] *= c_hi;
-        oacc[nt][3] *= c_hi;
+        for (int nt = 0; nt < NT; ++nt) {
+          oacc[nt][0] *= c_lo;
+          oacc[nt][1] *= c_lo;
+          oacc[nt][2] *= c_hi;
+          oacc[nt][3] *= c_hi;
+        }
       }
       const unsigned char* v_at = ks + (size_t)(((lane >> 3) & 1) * 8 + (lane & 7)) * k_stride + (col_w + (lane >> 4) * 8) * 2;
       const size_t p_at = (size_t)(wm * 16 + (lane & 15)) * P_STRIDE + (lane >> 4) * 16;
