@@ -207,3 +207,24 @@ def test_command_line_writes_a_model_folder_that_the_loader_accepts(tmp_path):
         assert tuple(ck.meta("l0.norm1.alpha")[1]) == () and tuple(ck.meta("l2.mix.sink")[1]) == (5,)
     finally:
         ck.close()
+
+
+def test_bench_design_option_builds_both_models_at_equal_size():
+    import bench
+    name, ours_of, (other, theirs_of), _ = bench.DESIGNS["zafopel"]
+    assert name == "Zafopel" and other == "lfm2_moe"
+    for width, layers, ff in bench.DESIGN_SIZES.values():
+        ours = build_model(ours_of(width, layers, ff), "bfloat16")
+        theirs = build_model(theirs_of(width, layers, ff), "bfloat16")
+        assert len(ours.run) == len(theirs.run) == layers
+        assert ours.spec.hidden_size == theirs.spec.hidden_size == width
+        mixers = [b.mixer for b in ours.blocks]
+        assert {m.sink_on for m in mixers} == {True, False} and any(m.window for m in mixers)
+        assert all(m.num_heads == theirs.blocks[0].mixer.num_heads for m in mixers)
+        kinds = [type(b.ffn).__name__ for b in ours.blocks]
+        assert kinds[0] == "MLP" and set(kinds[1:]) == {"SigmoidMoE"}
+        routed, theirs_routed = ours.blocks[1].ffn, theirs.blocks[1].ffn
+        assert (routed.num_experts, routed.top_k, routed.intermediate_size) == \
+               (theirs_routed.num_experts, theirs_routed.top_k, theirs_routed.intermediate_size)
+        if layers > 5:
+            assert any(e.cache_of is not None for e in ours.run)
