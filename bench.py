@@ -133,7 +133,7 @@ def _zafopel(width: int, layers: int, ff: int, vocab: int = 65536) -> dict:
     for i in range(layers):
         mlp = {"kind": "dense", "ff": ff} if i == 0 else routed
         if i % 4 == 1:
-            mixer = dict(common, mask={"size": 2048}, rot={"dims": 64, "base": 250000.0})
+            mixer = dict(common, mask={"size": 2048}, rot={"dims": 64, "base": 500000.0})
             if last_window is not None:
                 mixer["kv_from"], last_window = last_window, None
             else:
@@ -141,7 +141,7 @@ def _zafopel(width: int, layers: int, ff: int, vocab: int = 65536) -> dict:
             out.append({"type": "latent_attention", "mixer": mixer, "mlp": mlp})
         else:
             out.append({"type": "latent_attention_2", "mlp": mlp,
-                        "mixer": dict(common, q_rank=width // 2, rot={"dims": 64, "base": 10000.0})})
+                        "mixer": dict(common, q_rank=width // 2, rot={"dims": 64, "base": 100000.0})})
     return {"architecture": "Zafopel", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
             "layers": json.loads(json.dumps(out))}
 

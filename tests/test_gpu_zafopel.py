@@ -56,7 +56,7 @@ ALONE = {
     "window_part_of_the_slice_turns": [cases.window_layer(rot_dim=12, rot_dims=4, kv_rank=36, window=64)],
     "causal_without_a_mask": [cases.window_layer(window=None, mlp=cases.dense(24))],
     "sink_dense": [cases.sink_layer()],
-    "sink_wide_latent": [cases.sink_layer(heads=3, dim=32, rot_dim=8, vdim=16, kv_rank=136, q_rank=20,
+    "sink_wide_latent": [cases.sink_layer(heads=3, dim=32, rot_dim=8, vdim=16, kv_rank=160, q_rank=20,
                                           mlp=cases.moe(16, 4, 4))],
     "sink_odd": [cases.sink_layer(heads=7, dim=4, rot_dim=2, vdim=6, kv_rank=10, q_rank=6, mlp=None)],
     "reader": [cases.window_layer(window=11), cases.window_layer(window=30, kv_from=0, mlp=None)],

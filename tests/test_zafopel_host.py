@@ -102,7 +102,7 @@ def test_missing_and_unexpected_tensors_are_listed():
     assert "l2.mix.sink" in str(e.value) and "l3.mix.dkv" in str(e.value)
 
 
-@pytest.mark.parametrize("base,dims", [(300.0, 8), (10000.0, 16), (250000.0, 6), (2.0, 2)])
+@pytest.mark.parametrize("base,dims", [(300.0, 8), (5000.0, 16), (500000.0, 6), (2.0, 2)])
 def test_paired_rotary_table_follows_the_formula(base, dims):
     got, n = PairedRotaryPosition(head_dim=dims + 4, theta=base, rot_dim=dims).rotary("cpu")
     assert n == dims and got.dtype == torch.float32 and got[0] == 1.0

@@ -31,7 +31,7 @@ def window_layer(heads=3, dim=24, rot_dim=8, vdim=20, kv_rank=40, window=21, bas
     return {"type": "latent_attention", "mixer": mixer, "mlp": moe() if mlp == "moe" else mlp}
 
 
-def sink_layer(heads=2, dim=16, rot_dim=16, vdim=24, kv_rank=48, q_rank=28, base=10000.0, rot_dims=None, scale=None,
+def sink_layer(heads=2, dim=16, rot_dim=16, vdim=24, kv_rank=48, q_rank=28, base=5000.0, rot_dims=None, scale=None,
                mlp="dense"):
     """latent_attention_2: queries through a latent, causal, a sink per head."""
     mixer = {"heads": heads, "dim": dim, "rot_dim": rot_dim, "vdim": vdim, "kv_rank": kv_rank, "q_rank": q_rank,
