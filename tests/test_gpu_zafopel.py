@@ -61,13 +61,19 @@ ALONE = {
     "sink_odd": [cases.sink_layer(heads=7, dim=4, rot_dim=2, vdim=6, kv_rank=10, q_rank=6, mlp=None)],
     "reader": [cases.window_layer(window=11), cases.window_layer(window=30, kv_from=0, mlp=None)],
     "reader_sees_every_key": [cases.window_layer(window=9, mlp=None), cases.window_layer(window=None, kv_from=0)],
+    # sizes that are multiples of nothing: the products leave the tensor cores, the gate its fused store
+    "odd_sizes": [cases.sink_layer(heads=3, dim=12, rot_dim=6, vdim=10, kv_rank=20, q_rank=10, mlp=cases.moe(20, 3, 2)),
+                  cases.window_layer(heads=5, dim=6, rot_dim=2, vdim=14, kv_rank=22, window=7, mlp=cases.moe(12, 7, 3)),
+                  cases.window_layer(heads=5, dim=10, rot_dim=2, vdim=6, kv_rank=22, window=150, kv_from=1,
+                                     mlp=cases.dense(30)),
+                  cases.sink_layer(heads=33, dim=8, rot_dim=16, vdim=8, kv_rank=32, q_rank=40, mlp=cases.moe(8, 2, 2))],
 }
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", list(ALONE))
 def test_each_mechanism_alone(name, dtype):
-    cfg = cases.config(ALONE[name])
+    cfg = cases.config(ALONE[name], **({"width": 36, "vocab": 50} if name == "odd_sizes" else {}))
     tensors = cases.draw_weights(cfg, seed=len(name))
     tokens = cases.tokens_for(cfg, 70)
     model = load(cfg, tensors, dtype)
