@@ -418,16 +418,19 @@ __global__ void __launch_bounds__(128 * MTB, (KT == 32 && MTB == 1) ? 2 : 1) lat
   const int t_first = (lo / KT) * KT;
   const int ntiles = (hi - t_first) / KT + 1;
 
-  // a warp brings whole key rows in: one page lookup per row, the lanes its 16-byte pieces
+  // a warp brings whole key rows in, the lanes a row's 16-byte pieces.  Tiles start at multiples of KT, so with
+  // pages of a multiple of KT keys a tile lies in one page: one look-up and one division per tile, not per row
+  const bool one_page = page_size % KT == 0;
   auto issue = [&](int tile) {
     if (tile < ntiles) {
       const int t0 = t_first + tile * KT;
       unsigned char* ks = lm_raw + (size_t)(tile & 1) * stage_bytes;
+      const size_t row0 = one_page ? (size_t)bt[t0 / page_size] * page_size + t0 % page_size : 0;
       for (int j = warp; j < KT; j += 4 * MTB) {
         const int kp = t0 + j;
         const bool valid = kp >= lo && kp <= hi;
         const bf16* src = pool;
-        if (valid) src = pool + ((size_t)bt[kp / page_size] * page_size + kp % page_size) * kw;
+        if (valid) src = pool + (one_page ? row0 + j : (size_t)bt[kp / page_size] * page_size + kp % page_size) * kw;
         unsigned char* dst = ks + (size_t)j * k_stride;
         for (int c = lane; c < per; c += 32) la_cp_async16(dst + c * 16, valid ? src + c * 8 : src, valid);
       }
