@@ -1292,8 +1292,8 @@ def latent_prepare(q, q_off, kv, kv_off, c_gamma, eps, inv_freq, rot, positions,
 
 def latent_attention_tile_rows(H: int, r: int, rd: int, dtype) -> int:
     """Rows of one request that a block of ``latent_attention`` serves beside each other for ``H`` heads over
-    rows of r + rd (bfloat16 with r and rd multiples of 16 runs on the tensor cores, 32 units a block; everything
-    else on the CUDA cores, 16 units)."""
+    rows of r + rd (bfloat16 with r and rd multiples of 16 runs on the tensor cores, up to 64 (row, head) units a
+    block; everything else on the CUDA cores, 16 units)."""
     return int(fn("snk_latent_attention_tile_rows")(int(H), int(r), int(rd), code_of(dtype)))
 
 
